@@ -2,7 +2,7 @@
 
 Cache slots (one per schedule entry that writes a cache) with the same need (kv heads, head size, window) form a
 *group*. A group has its own pages: one pool tensor `(slots, pages, 2, kv_heads, page_size, head_dim)` (keys at index
-0, values at 1 of the third axis) and one block table per request, shared by the group's slots, so a page id means the
+0, values at 1 of the third axis; a `LatentNeed` group holds `(slots, pages, page_size, width)`, one vector per token) and one block table per request, shared by the group's slots, so a page id means the
 same page in every slot of the group (the reference keeps one table for all layers: fusezap/serve/kv_cache.py:436-460).
 A full group keeps every page until the request ends; a window group gives back the pages that lie wholly before the
 window of the request's next position (their table entries become -1) as soon as `commit` says how far the request is
@@ -32,6 +32,27 @@ class KVNeed:
     window: int = 0
 
 
+    def pool_shape(self, slots: int, pages: int, page_size: int) -> tuple[int, ...]:
+        return (slots, pages, 2, self.num_kv_heads, page_size, self.head_dim)
+
+    def views(self, slot_pool: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor | None]:
+        return slot_pool[:, 0], slot_pool[:, 1]
+
+
+@dataclass(frozen=True)
+class LatentNeed:
+    """A cache of one vector per token that every head reads: `width` values (a latent from which a mixer derives keys
+    and values, with whatever it stores beside it), no separate values. Pool `(slots, pages, page_size, width)`."""
+    width: int
+    window: int = 0
+
+    def pool_shape(self, slots: int, pages: int, page_size: int) -> tuple[int, ...]:
+        return (slots, pages, page_size, self.width)
+
+    def views(self, slot_pool: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor | None]:
+        return slot_pool, None
+
+
 @dataclass
 class KVGroup:
     need: KVNeed
@@ -39,7 +60,7 @@ class KVGroup:
     num_pages: int
     slots: list[int]                              # cache slot ids that live in this group
     max_pages_per_request: int = 0
-    pool: torch.Tensor | None = None              # (len(slots), num_pages, 2, Hkv, page_size, hd)
+    pool: torch.Tensor | None = None              # `need.pool_shape(len(slots), num_pages, page_size)`
     allocator: PageAllocator = field(init=False)
     # request -> int32 row of page ids by page index (-1: given back, or not yet there) and how many entries are in use.
     # Entries below the first live page are -1; every entry from there to `lens[req]` holds a page.
@@ -98,10 +119,10 @@ class KVGroup:
             held = row[:n]
             self.allocator.free(held[held >= 0].tolist())
 
-    def view(self, slot: int) -> tuple[torch.Tensor, torch.Tensor]:
-        """(keys, values) of one cache slot, each (num_pages, Hkv, page_size, hd) strided views of the pool."""
-        s = self.pool[self.slots.index(slot)]
-        return s[:, 0], s[:, 1]
+    def view(self, slot: int) -> tuple[torch.Tensor, torch.Tensor | None]:
+        """(keys, values) of one cache slot: for a `KVNeed` each a (num_pages, Hkv, page_size, hd) strided view of the
+        pool; for a `LatentNeed` the slot's (num_pages, page_size, width) and None."""
+        return self.need.views(self.pool[self.slots.index(slot)])
 
 
 def state_shape_dtype(need: Any) -> tuple[tuple[int, ...], torch.dtype]:
@@ -143,7 +164,7 @@ class StateSlots:
 
 
 class CacheManager:
-    def __init__(self, needs: dict[int, KVNeed], state_needs: dict[tuple[int, str], tuple[int, ...]], page_size: int,
+    def __init__(self, needs: "dict[int, KVNeed | LatentNeed]", state_needs: dict[tuple[int, str], tuple[int, ...]], page_size: int,
                  num_pages: int, max_requests: int, max_model_len: int, dtype: torch.dtype,
                  device: torch.device | str, allocate: bool = True):
         """needs: cache slot id -> KVNeed. state_needs: (schedule entry, name) -> shape of one request's state (float32),
@@ -164,8 +185,7 @@ class CacheManager:
         self.states = StateSlots(max_requests)
         if allocate:
             for grp in self.groups:
-                grp.pool = torch.zeros((len(grp.slots), num_pages, 2, grp.need.num_kv_heads, page_size, grp.need.head_dim),
-                                       dtype=dtype, device=self.device)
+                grp.pool = torch.zeros(grp.need.pool_shape(len(grp.slots), num_pages, page_size), dtype=dtype, device=self.device)
             for key, need in state_needs.items():
                 shape, state_dtype = state_shape_dtype(need)
                 self.states.tensors[key] = torch.zeros((max_requests, *shape), dtype=state_dtype, device=self.device)

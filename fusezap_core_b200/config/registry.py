@@ -33,6 +33,15 @@ register_architecture("llama", _dense)
 register_architecture("qwen2", _dense)
 
 
+def _pepilix(c: dict):
+    from .pepilix import PepilixConfig
+    cfg = PepilixConfig.from_json(c)
+    return cfg, cfg.spec()
+
+
+register_architecture("Pepilix", _pepilix)
+
+
 def read_config_json(model_dir: str) -> dict:
     path = os.path.join(model_dir, "config.json")
     if not os.path.isfile(path):
@@ -52,9 +61,14 @@ def read_config_json(model_dir: str) -> dict:
     return config
 
 
+def architecture_name(config: dict) -> str:
+    """The registry key of a config.json: `model_type`, else `architecture` (a single name), else `llama`."""
+    return config.get("model_type") or config.get("architecture") or "llama"
+
+
 def describe(config: dict) -> tuple[Any, ModelSpec]:
     """config.json dict -> (typed config, validated ModelSpec) through the registry."""
-    name = config.get("model_type", "llama")
+    name = architecture_name(config)
     if name not in ARCHITECTURES:
         raise NotImplementedError(f"model_type {name!r} is not supported (have {sorted(ARCHITECTURES)})")
     typed, spec = ARCHITECTURES[name](config)

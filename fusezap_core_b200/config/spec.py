@@ -34,7 +34,7 @@ class LayerSpec:
     prefix: str
     block: PartSpec
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: PartSpec | None              # None: the layer has no feed-forward (its block must be one that takes none)
     norm: PartSpec | None = None
 
 

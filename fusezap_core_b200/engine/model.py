@@ -21,7 +21,7 @@ def build_layers(spec: ModelSpec) -> list[Any]:
     layers = []
     for ls in spec.layers:
         mixer = build(MIXERS, "mixer", ls.mixer)
-        ffn = build(FEED_FORWARDS, "feed-forward", ls.ffn)
+        ffn = build(FEED_FORWARDS, "feed-forward", ls.ffn) if ls.ffn is not None else None   # a layer may have none
         if ls.block.kind not in BLOCKS:
             raise NotImplementedError(f"block kind {ls.block.kind!r} is not registered (have {sorted(BLOCKS)})")
         layers.append(BLOCKS[ls.block.kind](mixer, ffn, _norm_maker(ls), **ls.block.params))
@@ -62,6 +62,12 @@ def optional_groups_to_write(typed: Any, spec: ModelSpec) -> set[str]:
     return set() if spec.tie_embeddings else {"lm_head"}
 
 
+def _state_need(block: Any) -> dict[str, Any]:
+    """The per-request state one execution of a layer keeps: what its block declares (a block's default is its mixer's)."""
+    own = getattr(block, "state_need", None)
+    return own() if own is not None else block.mixer.state_need()
+
+
 class DecoderModel:
     def __init__(self, spec: ModelSpec, typed: Any = None):
         spec.validate()
@@ -97,7 +103,7 @@ class DecoderModel:
     def state_needs(self) -> dict[tuple[int, str], Any]:
         """(schedule entry, name) -> what the mixer declares: a shape (float32), or (shape, torch dtype)."""
         return {(n, name): need for n, e in enumerate(self.spec.schedule)
-                for name, need in self.layers[e.layer].mixer.state_need().items()}
+                for name, need in _state_need(self.layers[e.layer]).items()}
 
     def graph_safe(self) -> bool:
         """True if every part's forward is a fixed sequence of kernels over device data (see `Part.graph_safe`)."""
@@ -119,7 +125,7 @@ class DecoderModel:
             if children is not None:
                 stack += [c for _, c in children()]
             for name in ("mixer", "ffn"):          # a block that does not list its children still has these two
-                if hasattr(p, name):
+                if getattr(p, name, None) is not None:
                     stack.append(getattr(p, name))
         return out
 
@@ -209,7 +215,11 @@ def random_model(config: dict, dtype: str = "bfloat16", device: str | torch.devi
         if p.ignore or (p.group is not None and p.group not in groups):
             continue
         if p.role == "int_table":
-            tensors[name] = torch.zeros(p.shape, dtype=torch.int32, device=device)
+            if p.high:      # every row holds distinct values below `high`
+                order = torch.rand((p.shape[0], p.high), generator=gen, device=device).argsort(1)
+                tensors[name] = order[:, :p.shape[1]].to(torch.int32).contiguous()
+            else:
+                tensors[name] = torch.zeros(p.shape, dtype=torch.int32, device=device)
             continue
         if p.init == "ones":
             t = torch.ones(p.shape, dtype=torch.float32, device=device)

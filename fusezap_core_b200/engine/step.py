@@ -10,7 +10,7 @@ Per step the host packs one int32 block and copies it to the device once:
   tokens[N] | pos[N] | seq_row[N] | src[N] | sel[R] | segments[S x 4] | one block table (S x MB) per cache group | extra
 seq_row[n] is the row of the request's block table in this step (-1: padding row), sel the rows whose logits are
 wanted (-1: none), a segment is (first row, rows, first position, state slot) of one request's portion. `extra` belongs
-to the kernel table: the mixers of the model say what kinds of step data their kernels need (`Mixer.step_needs()`), the
+to the kernel table: the parts of the model say what kinds of step data their kernels need (`Part.step_needs()`), the
 table says how many int32 it wants for them (`Ops.step_extra_ints`) and fills them when the step is packed
 (`Ops.plan_step`), before the one copy. The step function itself knows nothing of any kernel's tiling.
 """
@@ -205,6 +205,8 @@ class StepContext:
     meta: StepMeta
     positions: dict[str, Any]
     model: DecoderModel
+    token_ids: torch.Tensor | None = None     # the step's token ids on the device, int32 (N,), for parts that declare
+                                              # the step need "token_ids"; set before the first layer runs
 
 
 class StepRunner:
@@ -215,7 +217,7 @@ class StepRunner:
         dev = model.device
         self.max_rows = max_rows
         # what kinds of step data the mixers' kernels need, and how many int32 the kernel table wants for them
-        self.needs = tuple(sorted({k for e in model.spec.schedule for k in model.layers[e.layer].mixer.step_needs()}))
+        self.needs = tuple(sorted({k for part in model.parts() for k in getattr(part, "step_needs", tuple)()}))
         max_segments = max_segments or max_rows
         extra = getattr(self.ops, "step_extra_ints", lambda *a: 0)(self.needs, max_rows, max_segments)
         self.meta = StepMeta(dev, max_rows, max_wanted or max_rows, max_segments, len(cache.groups),
@@ -256,6 +258,11 @@ class StepRunner:
             self.ops.embed(model.embed, meta.tokens, x, src, self.prev_ids, model.embed_scale)
         else:
             self.ops.embed(model.embed, meta.tokens, x, src, self.prev_ids)
+        if "token_ids" in self.needs:
+            ctx.token_ids = meta.tokens
+            if src is not None:      # some rows take their token from the ids the previous step left on the device
+                ctx.token_ids = self.ws.get("token_ids", (meta.n_rows,), torch.int32)
+                self.ops.select_tokens(meta.tokens, src, self.prev_ids, ctx.token_ids)
         delta = None
         for e, lc in zip(spec.schedule, self.layer_caches):
             x, delta = model.layers[e.layer].forward(ctx, x, delta, lc)

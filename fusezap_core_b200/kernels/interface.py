@@ -21,7 +21,7 @@ class Ops:
 
     def step_extra_ints(self, needs: tuple, max_rows: int, max_segments: int) -> int:
         """How many int32 of the step's metadata block this table wants for itself, given the kinds of step data the
-        model's mixers need (`Mixer.step_needs()`), for steps of at most max_rows rows of at most max_segments requests."""
+        model's parts need (`Part.step_needs()`), for steps of at most max_rows rows of at most max_segments requests."""
         return 0
 
     def plan_step(self, meta: Any, needs: tuple) -> None:
@@ -44,9 +44,83 @@ class Ops:
         raise NotImplementedError
 
     def add_rmsnorm(self, x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
-                    h: torch.Tensor, rows: torch.Tensor | None = None) -> None:
+                    h: torch.Tensor, rows: torch.Tensor | None = None, groups: int = 1) -> None:
         """rows None: x += delta (if given), in place; h[n] = T(weight * x[n] / sqrt(mean(x[n]^2) + eps)).
-        rows (int32 (R,), -1 = none): h[r] is computed from x[rows[r]] + delta[rows[r]]; x is not written."""
+        rows (int32 (R,), -1 = none): h[r] is computed from x[rows[r]] + delta[rows[r]]; x is not written.
+        groups > 1: the row is split into that many equal consecutive parts and the mean is taken over each part alone."""
+        raise NotImplementedError
+
+    def select_tokens(self, tokens: torch.Tensor, src: torch.Tensor, prev_ids: torch.Tensor, out: torch.Tensor) -> None:
+        """out[n] = prev_ids[src[n]] if src[n] >= 0 else tokens[n] (all int32): the ids `embed` reads, as one tensor."""
+        raise NotImplementedError
+
+    def short_conv(self, h: torch.Tensor, w: torch.Tensor, state: torch.Tensor | None, meta: Any, out: torch.Tensor,
+                   residual: bool = True) -> None:
+        """Causal convolution over time within each portion of the step (meta.seg: first row, rows, first position,
+        state slot). h, out: (N, C) T; w: (C, taps) T; state: (slots, taps - 1, C) float32, the last taps - 1 inputs of
+        each request so far, oldest first. For the row at place i of its portion:
+        out = (h if residual) + sum_j w[:, j] * in(i - taps + 1 + j), in(k) = h[first row + k] for k >= 0, else
+        state[slot, taps - 1 + k]. The sum is float32, j rising, rounded once. Afterwards state[slot] holds the portion's
+        request's last taps - 1 inputs. Padding rows give zeros."""
+        raise NotImplementedError
+
+    def gated_sum(self, a: torch.Tensor, gate_a: torch.Tensor | None, f: torch.Tensor | None, gate_f: torch.Tensor | None,
+                  out: torch.Tensor, f_terms: int = 1, f_weight: float = 1.0) -> None:
+        """out[n] = a[n] * sigmoid(gate_a[n]) + (f_weight * sum_k f[n * f_terms + k]) * sigmoid(gate_f[n]); all float32,
+        (N, D), f (N * f_terms, D), the terms added in rising k. A gate that is None counts as 1, f None as no second
+        term. sigmoid(z) = 1 / (1 + exp(-z))."""
+        raise NotImplementedError
+
+    def scale_(self, x: torch.Tensor, factor: float) -> None:
+        """x *= factor, float32, in place."""
+        raise NotImplementedError
+
+    def check_latent_attention(self, num_heads: int, key_width: int, value_width: int) -> None:
+        """Raise ValueError if `latent_attention` cannot take these sizes."""
+        raise NotImplementedError
+
+    def latent_cache_write(self, down: torch.Tensor, norm_weight: torch.Tensor, eps: float, cos: torch.Tensor,
+                           sin: torch.Tensor, rotated: int, meta: Any, cache: Any) -> None:
+        """down: (N, L + R) float32, cache.keys: (pages, page_size, L + R) T. For every live row: the first L values
+        are divided by their root mean square (eps inside the root) and multiplied by norm_weight (L,); of the last R,
+        the first `rotated` are turned by the row's position (pairs i, i + rotated/2, tables (max_len, rotated/2)), the
+        rest pass; the L + R values are rounded once and stored at the row's place in its request's pages."""
+        raise NotImplementedError
+
+    def rotate_heads(self, q: torch.Tensor, offset: int, cos: torch.Tensor, sin: torch.Tensor, rotated: int, meta: Any,
+                     out: torch.Tensor, out_offset: int) -> None:
+        """q: (N, H, W) T, out: (N, H, Wo) T. out[n, h, out_offset : out_offset + W - offset] = q[n, h, offset:] with its
+        first `rotated` values turned by the row's position (as in `latent_cache_write`); float32 arithmetic."""
+        raise NotImplementedError
+
+    def linear_heads(self, a: torch.Tensor, a_offset: int, k: int, w: torch.Tensor, out: torch.Tensor,
+                     out_offset: int) -> None:
+        """One product per head: out[n, h, out_offset : out_offset + M] = w[h] . a[n, h, a_offset : a_offset + k];
+        a: (N, H, Wa) T, w: (H, M, k) T, out: (N, H, Wo) T; float32 accumulation over k in rising order."""
+        raise NotImplementedError
+
+    def latent_attention(self, q: torch.Tensor, cache: Any, meta: Any, out: torch.Tensor, value_width: int, scale: float,
+                         window: int) -> None:
+        """q: (N, H, W) T; cache.keys: (pages, page_size, W) T, one vector e_j per cached token, shared by all heads.
+        out[n, h] = sum_j softmax_j((q[n, h] . e_j) * scale) e_j[:value_width] over the keys j of the row's own request
+        with max(0, p - window + 1) <= j <= p (window 0: 0 <= j <= p), p = meta.pos[n]; out: (N, H, value_width) T."""
+        raise NotImplementedError
+
+    def route_by_table(self, token_ids: torch.Tensor, meta: Any, table: torch.Tensor, num_experts: int) -> Any:
+        """table: (V, top) int32. Groups the step's (row, choice) pairs by expert table[token_ids[row], choice] (padding
+        rows have none). Returns what `grouped_linear_glu` / `grouped_linear_scatter` need, valid until the next call."""
+        raise NotImplementedError
+
+    def grouped_linear_glu(self, h: torch.Tensor, w: torch.Tensor, route: Any, y: torch.Tensor, alpha: float,
+                           limit: float) -> None:
+        """w: (E, 2 I, K): expert e's gate rows, then its up rows. For every pair (row n, expert e) of the route:
+        g = min(w[e, :I] . h[n], limit), u = clamp(w[e, I:] . h[n], -limit, limit), y[pair] = T(g * sigmoid(alpha * g) *
+        (u + 1)); y: (N * top, I) T in the route's own order of pairs; products and activation in float32."""
+        raise NotImplementedError
+
+    def grouped_linear_scatter(self, y: torch.Tensor, w: torch.Tensor, route: Any, out: torch.Tensor) -> None:
+        """w: (E, D, I). out[n * top + k] = w[e] . y[pair], float32 (N * top, D), for the pair of row n's k-th choice;
+        rows of padding are zero."""
         raise NotImplementedError
 
     def linear(self, a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> None:

@@ -22,7 +22,7 @@ from typing import Any, Callable, TYPE_CHECKING
 
 import torch
 
-from ..cache import KVNeed
+from ..cache import KVNeed, LatentNeed
 from ..config import PartSpec
 from ..weights import ParamSpec
 
@@ -64,8 +64,9 @@ def build(table: dict[str, type], what: str, spec: PartSpec) -> Any:
 @dataclass
 class LayerCache:
     """What one schedule entry's mixer sees of the cache manager."""
-    keys: torch.Tensor | None = None        # (pages, Hkv, page_size, hd) view of this entry's cache slot
-    values: torch.Tensor | None = None
+    keys: torch.Tensor | None = None        # (pages, Hkv, page_size, hd) view of this entry's cache slot; for a
+                                            # `LatentNeed` the slot's (pages, page_size, width) vectors
+    values: torch.Tensor | None = None      # None for a `LatentNeed`
     group: int = -1                         # index of the block-table set in the step metadata
     page_size: int = 0
     write: bool = True                      # False: read what the slot's owner wrote earlier in this step
@@ -84,6 +85,12 @@ class Part:
     def bind(self, tensors: dict[str, torch.Tensor], ops: Any) -> None:
         """Receives the tensors of `tensors()` that the checkpoint has (optional ones may be absent)."""
 
+    def step_needs(self) -> tuple[str, ...]:
+        """Kinds of per-step data this part's kernels need beside the common metadata: "attention" (the kernel table
+        plans its attention kernels' tiles for every step), "token_ids" (the step's token ids as one device tensor,
+        `ctx.token_ids`, also where a token comes from the ids the previous step left on the device). None by default."""
+        return ()
+
     def weight_tensors(self) -> list[torch.Tensor]:
         """Every device tensor a step reads once for this part (sub-parts not included): what the decode roofline counts
         as this part's weight bytes. The default finds the tensors the part keeps as attributes (alone, or in tuples
@@ -98,7 +105,7 @@ class Part:
 
 
 class Mixer(Part):
-    def cache_need(self) -> KVNeed | None:
+    def cache_need(self) -> "KVNeed | LatentNeed | None":
         return None
 
     def state_need(self) -> dict[str, Any]:
@@ -107,11 +114,6 @@ class Mixer(Part):
 
     def position_name(self) -> str | None:
         return None
-
-    def step_needs(self) -> tuple[str, ...]:
-        """Kinds of per-step data this mixer's kernels need beside the common metadata (for instance "attention": the
-        kernel table then plans its attention kernels' tiles for every step). None by default."""
-        return ()
 
     def forward(self, ctx: "StepContext", h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         raise NotImplementedError
@@ -150,6 +152,10 @@ class Block(Part):
     prefix, part) of everything it holds."""
     def children(self) -> tuple:
         return ()
+
+    def state_need(self) -> dict[str, Any]:
+        """Per-request state of one execution of the layer: the mixer's, plus whatever the block itself carries."""
+        return self.mixer.state_need()
 
     def forward(self, ctx: "StepContext", x: torch.Tensor, delta: torch.Tensor | None,
                 cache: LayerCache) -> tuple[torch.Tensor, torch.Tensor | None]:

@@ -3,7 +3,8 @@
 `x <- x + delta` (the pending term of the previous sublayer), then `h = w * (x / sqrt(mean(x^2) + eps))`
 (fusezap/serve/models/llama.py:500-503, 508-523: `mean = sum * (1/D)`, the fused kernel also writes the residual
 stream). The residual stream x is float32 in both dtypes; the sum of squares, the scale and the weight product are
-computed in 32-bit and h is rounded once to the activation dtype.
+computed in 32-bit and h is rounded once to the activation dtype. With `groups` > 1 the vector is normed in that many
+equal consecutive parts, each by its own mean square; the weight still spans the whole vector.
 """
 from __future__ import annotations
 import torch
@@ -14,18 +15,33 @@ from .base import Norm, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    def __init__(self, size: int, eps: float):
-        self.size, self.eps = size, float(eps)
+    def __init__(self, size: int, eps: float, groups: int = 1, name: str = "weight"):
+        """groups: the vector is split into this many equal consecutive parts and each is divided by its own root mean
+        square (1: the whole vector). name: the weight's tensor name relative to the part ("" when the part's prefix is
+        the whole name)."""
+        if groups <= 0 or size % groups:
+            raise ValueError(f"a norm over {size} values cannot be split into {groups} equal groups")
+        self.size, self.eps, self.groups, self.name = size, float(eps), int(groups), name
         self.weight: torch.Tensor | None = None
 
     def tensors(self) -> dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.size,), role="vector", init="ones")}
+        return {self.name: ParamSpec((self.size,), role="vector", init="ones")}
 
     def bind(self, tensors, ops) -> None:
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.name]
 
     def forward(self, ctx, x, delta, rows=None, n_rows=None):
         n = x.shape[0] if rows is None else (n_rows if n_rows is not None else rows.shape[0])
         h = ctx.ws.get("norm_h" if rows is None else "norm_h_rows", (n, self.size), ctx.ops.dtype)
-        ctx.ops.add_rmsnorm(x, delta, self.weight, self.eps, h, rows)
+        self._run(ctx, x, delta, h, rows)
         return h
+
+    def forward_into(self, ctx, x, h) -> None:
+        """h = norm(x), into a buffer of the caller's (a second norm of the same x needs one of its own)."""
+        self._run(ctx, x, None, h, None)
+
+    def _run(self, ctx, x, delta, h, rows) -> None:
+        if self.groups == 1:
+            ctx.ops.add_rmsnorm(x, delta, self.weight, self.eps, h, rows)
+        else:
+            ctx.ops.add_rmsnorm(x, delta, self.weight, self.eps, h, rows, groups=self.groups)

@@ -1,0 +1,87 @@
+"""Parallel block with gated sublayers: `x += g1 * mixer(h1') + g2 * ffn(h2)`, both sublayers reading the same x.
+
+`h1 = norm1(x)`, `h2 = norm2(x)`; the mixer reads `h1' = h1 + conv(h1)` when the block has a short convolution
+(`taps` > 1; see `short_conv.ShortConv`), else h1; with `gated` each sublayer's result is multiplied element by element by
+`sigmoid(W_g h + b_g)` of its own norm's output (before the convolution). A layer without a feed-forward has only the
+first term (and neither norm2 nor the second gate). The pending term of the previous layer is added by norm1, in the
+same pass over the row; gates, their sigmoid and the sum of the two terms are 32-bit.
+"""
+from __future__ import annotations
+import torch
+
+from ..weights import ParamSpec
+from .base import Block, FeedForward, LayerCache, Mixer, register_block
+from .short_conv import ShortConv
+
+_NAMES = {"norm1": "norm1", "norm2": "norm2", "mixer": "mixer", "ffn": "ffn", "conv": "conv", "gate1": "gate1",
+          "gate2": "gate2", "bias": "bias"}
+
+
+@register_block("parallel_gated")
+class ParallelGatedBlock(Block):
+    def __init__(self, mixer: Mixer, ffn: FeedForward | None, make_norm, hidden_size: int, taps: int = 1,
+                 gated: bool = True, norms: tuple = (None, None), names: dict | None = None):
+        self.mixer, self.ffn, self.D, self.gated = mixer, ffn, hidden_size, bool(gated)
+        self.names = {**_NAMES, **(names or {})}
+        self.norm1 = make_norm(norms[0]) if norms[0] is not None else make_norm()
+        self.norm2 = None
+        if ffn is not None:
+            self.norm2 = make_norm(norms[1]) if norms[1] is not None else make_norm()
+        self.conv = ShortConv(hidden_size, taps, name="") if taps > 1 else None
+        self.wg1 = self.bg1 = self.wg2 = self.bg2 = None
+
+    def children(self):
+        n = self.names
+        out = [(n["norm1"], self.norm1), (n["mixer"], self.mixer)]
+        if self.conv is not None:
+            out.append((n["conv"], self.conv))
+        if self.ffn is not None:
+            out += [(n["norm2"], self.norm2), (n["ffn"], self.ffn)]
+        return tuple(out)
+
+    def state_need(self) -> dict:
+        return {**self.mixer.state_need(), **(self.conv.state_need() if self.conv is not None else {})}
+
+    def tensors(self) -> dict[str, ParamSpec]:
+        out = {(f"{prefix}.{k}" if k else prefix): v for prefix, part in self.children() for k, v in part.tensors().items()}
+        if self.gated:
+            n, D = self.names, self.D
+            for g in ("gate1", "gate2") if self.ffn is not None else ("gate1",):
+                out[n[g]] = ParamSpec((D, D))
+                out[f"{n[g]}.{n['bias']}"] = ParamSpec((D,), role="vector", init="zeros")
+        return out
+
+    def bind(self, tensors, ops) -> None:
+        for prefix, part in self.children():
+            own = {k[len(prefix) + 1:]: v for k, v in tensors.items() if k == prefix or k.startswith(prefix + ".")}
+            part.bind(own, ops)
+        if self.gated:
+            n = self.names
+            self.wg1, self.bg1 = tensors[n["gate1"]], tensors[f"{n['gate1']}.{n['bias']}"].float()
+            if self.ffn is not None:
+                self.wg2, self.bg2 = tensors[n["gate2"]], tensors[f"{n['gate2']}.{n['bias']}"].float()
+
+    def forward(self, ctx, x, delta, cache: LayerCache):
+        n, ops, ws = x.shape[0], ctx.ops, ctx.ws
+        h1 = self.norm1.forward(ctx, x, delta)                      # x += pending term; h1 = norm1(x)
+        g1 = g2 = None
+        if self.gated:
+            g1 = ws.get("gate1", (n, self.D), torch.float32)
+            ops.linear(h1, self.wg1, self.bg1, g1)
+        hm = self.conv.forward(ctx, h1, cache.state.get("conv")) if self.conv is not None else h1
+        a = self.mixer.forward(ctx, hm, cache)
+        f, f_terms, f_weight = None, 1, 1.0
+        if self.ffn is not None:
+            h2 = ws.get("norm_h2", (n, self.D), ops.dtype)
+            self.norm2.forward_into(ctx, x, h2)
+            if self.gated:
+                g2 = ws.get("gate2", (n, self.D), torch.float32)
+                ops.linear(h2, self.wg2, self.bg2, g2)
+            f = self.ffn.forward(ctx, h2)
+            if isinstance(f, tuple):          # (terms (N * k, D), k, weight): the feed-forward leaves its sum to the block
+                f, f_terms, f_weight = f
+        if not self.gated and f is None:
+            return x, a
+        out = ws.get("block_delta", (n, self.D), torch.float32)
+        ops.gated_sum(a, g1, f, g2, out, f_terms, f_weight)
+        return x, out

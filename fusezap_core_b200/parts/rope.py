@@ -40,17 +40,25 @@ def inverse_frequencies(head_dim: int, theta: float, kind: str = "default", fact
 class RotaryEncoding(PositionEncoding):
     def __init__(self, head_dim: int, theta: float, kind: str = "default", factor: float = 1.0,
                  low_freq_factor: float = 1.0, high_freq_factor: float = 4.0,
-                 original_max_position_embeddings: int = 0):
+                 original_max_position_embeddings: int = 0, precise: bool = False):
+        """precise: frequencies theta^(-2j/head_dim) and angles p * f_j are computed in 64-bit and the cosines and sines
+        rounded once to float32 (default: in float32 throughout, as the dense decoder's reference does)."""
         if head_dim % 2:
             raise ValueError(f"rope needs an even head_dim, got {head_dim}")
-        self.head_dim = head_dim
+        self.head_dim, self.precise = head_dim, bool(precise)
+        if precise and kind != "default":
+            raise NotImplementedError("precise angles are computed for unscaled frequencies only")
+        self.inv_freq64 = np.float64(theta) ** (-np.arange(0, head_dim, 2, dtype=np.float64) / np.float64(head_dim))
         self.inv_freq = inverse_frequencies(head_dim, theta, kind, factor, low_freq_factor, high_freq_factor,
                                             original_max_position_embeddings)
         self.cos: torch.Tensor | None = None
         self.sin: torch.Tensor | None = None
 
     def prepare(self, max_len: int, device: torch.device) -> None:
-        fr = np.arange(max_len, dtype=np.float32)[:, None] * self.inv_freq[None, :]
+        if self.precise:
+            fr = np.arange(max_len, dtype=np.float64)[:, None] * self.inv_freq64[None, :]
+        else:
+            fr = np.arange(max_len, dtype=np.float32)[:, None] * self.inv_freq[None, :]
         self.cos = torch.from_numpy(np.cos(fr).astype(np.float32)).to(device)
         self.sin = torch.from_numpy(np.sin(fr).astype(np.float32)).to(device)
 

@@ -1,0 +1,38 @@
+"""A short causal convolution over time, per channel, with the inputs it still needs kept as per-request state.
+
+`y_t = sum_j w[:, j] * h_(t - taps + 1 + j)`, j = 0 .. taps-1, with zeros before the sequence's start (so `w[:, taps-1]`
+multiplies the token's own input). A step may bring any portion of a sequence: the last `taps - 1` inputs of the
+sequence so far live in a state slot `(taps - 1, size)` (oldest first, zero when the request gets its slot), are read
+for the first rows of the portion and replaced by the portion's last inputs afterwards. The sum is in 32-bit, taps in
+rising j, and rounded once.
+"""
+from __future__ import annotations
+import torch
+
+from ..weights import ParamSpec
+from .base import Part
+
+
+class ShortConv(Part):
+    def __init__(self, size: int, taps: int, name: str = "weight", residual: bool = True):
+        """residual: the result is `h + conv(h)` (what a block hands on in place of h); False: `conv(h)` alone."""
+        if taps < 1:
+            raise ValueError(f"a convolution needs at least one tap, got {taps}")
+        self.size, self.taps, self.name, self.residual = size, int(taps), name, bool(residual)
+        self.weight: torch.Tensor | None = None
+
+    def tensors(self) -> dict[str, ParamSpec]:
+        return {self.name: ParamSpec((self.size, self.taps))}
+
+    def bind(self, tensors, ops) -> None:
+        self.weight = tensors[self.name]
+
+    def state_need(self) -> dict:
+        return {"conv": (self.taps - 1, self.size)} if self.taps > 1 else {}
+
+    def forward(self, ctx, h: torch.Tensor, state: torch.Tensor | None, tag: str = "conv_out") -> torch.Tensor:
+        """h: (N, size) T; state: (slots, taps - 1, size) float32 (None when taps == 1). Returns (N, size) T and leaves
+        the state of every portion's request at the portion's end."""
+        out = ctx.ws.get(tag, tuple(h.shape), h.dtype)
+        ctx.ops.short_conv(h, self.weight, state, ctx.meta, out, self.residual)
+        return out

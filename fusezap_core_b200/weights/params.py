@@ -11,3 +11,5 @@ class ParamSpec:
     init: str = "normal"          # "normal" (std 0.02), "ones", "zeros"
     group: str | None = None      # None: required. Otherwise the name of an all-or-none group of optional tensors
     ignore: bool = False          # accepted if present, never loaded (a tied model's stored output matrix)
+    high: int = 0                 # "int_table" only: the random-weights writer fills every row with distinct values
+                                  # drawn from range(high) (0: a table of zeros)

@@ -21,9 +21,18 @@ from .safetensors_io import write_file
 STD = 0.02
 
 
+def distinct_rows(rng: np.random.Generator, shape: tuple[int, ...], high: int) -> np.ndarray:
+    """An int32 table whose rows each hold distinct values of range(high) (zeros when high is 0)."""
+    if not high:
+        return np.zeros(shape, np.int32)
+    if len(shape) != 2 or shape[1] > high:
+        raise ValueError(f"an integer table of shape {shape} cannot hold distinct values below {high} in every row")
+    return np.argsort(rng.random((shape[0], high)), axis=1)[:, :shape[1]].astype(np.int32)
+
+
 def draw(rng: np.random.Generator, p: ParamSpec, norm_noise: bool, optional: bool) -> torch.Tensor:
     if p.role == "int_table":
-        return torch.zeros(p.shape, dtype=torch.int32)
+        return torch.from_numpy(distinct_rows(rng, p.shape, p.high))
     if p.init == "ones":
         a = np.ones(p.shape, np.float32)
         if norm_noise:

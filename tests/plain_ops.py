@@ -138,3 +138,123 @@ class PlainOps:
 
     def check_errors(self, copied: bool = False) -> None:
         pass
+
+
+class PlainOpsWide(PlainOps):
+    """The plain table with the operations of the gated parallel block, the latent attention and the table-routed
+    experts, written from their meanings in `kernels/interface.py`."""
+
+    def add_rmsnorm(self, x, delta, weight, eps, h, rows=None, groups=1) -> None:
+        if groups == 1:
+            return super().add_rmsnorm(x, delta, weight, eps, h, rows)
+        if rows is None:
+            if delta is not None:
+                x.add_(delta)
+            src = x
+        else:
+            r = rows.long().clamp(min=0)
+            src = x[r] + (delta[r] if delta is not None else 0)
+        parts = src.view(src.shape[0], groups, -1)
+        y = (parts * torch.rsqrt((parts * parts).mean(-1, keepdim=True) + eps)).reshape(src.shape) * weight.float()
+        if rows is not None:
+            y = torch.where((rows < 0)[:, None], torch.zeros_like(y), y)
+        h.copy_(y.to(h.dtype))
+
+    def select_tokens(self, tokens, src, prev_ids, out) -> None:
+        out.copy_(torch.where(src >= 0, prev_ids[src.long().clamp(min=0)], tokens))
+
+    def short_conv(self, h, w, state, meta, out, residual=True) -> None:
+        taps = w.shape[1]
+        out.zero_()
+        wf = w.float()
+        for sg in meta.segments:
+            rows = h[sg.row0: sg.row0 + sg.n].float()
+            before = state[sg.state_slot] if taps > 1 else rows[:0]
+            line = torch.cat([before, rows], 0)                      # inputs taps-1 back from the portion's start
+            acc = rows.clone() if residual else torch.zeros_like(rows)
+            y = torch.zeros_like(rows)
+            for j in range(taps):
+                y = y + wf[:, j] * line[j: j + sg.n]
+            out[sg.row0: sg.row0 + sg.n] = (acc + y).to(out.dtype)
+            if taps > 1:
+                state[sg.state_slot] = line[line.shape[0] - (taps - 1):]
+
+    def gated_sum(self, a, gate_a, f, gate_f, out, f_terms=1, f_weight=1.0) -> None:
+        sig = lambda z: 1.0 / (1.0 + torch.exp(-z))
+        y = a * sig(gate_a) if gate_a is not None else a.clone()
+        if f is not None:
+            t = f.view(a.shape[0], f_terms, -1).sum(1) * torch.tensor(f_weight, dtype=torch.float32)
+            y = y + (t * sig(gate_f) if gate_f is not None else t)
+        out.copy_(y)
+
+    def scale_(self, x, factor) -> None:
+        x.mul_(factor)
+
+    def check_latent_attention(self, num_heads, key_width, value_width) -> None:
+        if value_width > key_width:
+            raise ValueError("the value part cannot be wider than the cached vector")
+
+    def _turn(self, v, cos, sin, rotated, pos):
+        half = rotated // 2
+        c, s = cos[pos], sin[pos]
+        while c.dim() < v.dim():
+            c, s = c.unsqueeze(1), s.unsqueeze(1)
+        a, b = v[..., :half], v[..., half:rotated]
+        return torch.cat([a * c - b * s, b * c + a * s, v[..., rotated:]], -1)
+
+    def latent_cache_write(self, down, norm_weight, eps, cos, sin, rotated, meta, cache) -> None:
+        L = norm_weight.shape[0]
+        pos, row = meta.pos.long(), meta.seq_row.long()
+        c = down[:, :L]
+        c = c * torch.rsqrt((c * c).mean(-1, keepdim=True) + eps) * norm_weight.float()
+        e = torch.cat([c, self._turn(down[:, L:], cos, sin, rotated, pos)], -1).to(cache.keys.dtype)
+        table, bs = meta.table(cache.group), cache.page_size
+        for i in range(down.shape[0]):
+            if row[i] < 0:
+                continue
+            page = int(table[row[i], pos[i] // bs])
+            assert page >= 0, f"row {i} at position {int(pos[i])} has no page"
+            cache.keys[page, pos[i] % bs] = e[i]
+
+    def rotate_heads(self, q, offset, cos, sin, rotated, meta, out, out_offset) -> None:
+        v = self._turn(q[..., offset:].float(), cos, sin, rotated, meta.pos.long())
+        v = torch.where((meta.seq_row >= 0)[:, None, None], v, torch.zeros(()))
+        out[..., out_offset: out_offset + v.shape[-1]] = v.to(out.dtype)
+
+    def linear_heads(self, a, a_offset, k, w, out, out_offset) -> None:
+        y = torch.einsum("nhk,hmk->nhm", a[..., a_offset: a_offset + k].float(), w.float())
+        out[..., out_offset: out_offset + w.shape[1]] = y.to(out.dtype)
+
+    def latent_attention(self, q, cache, meta, out, value_width, scale, window) -> None:
+        pos, row = meta.pos.long(), meta.seq_row.long()
+        table, bs = meta.table(cache.group), cache.page_size
+        out.zero_()
+        for i in range(q.shape[0]):
+            if row[i] < 0:
+                continue
+            p = int(pos[i])
+            js = torch.arange(max(0, p - window + 1) if window else 0, p + 1)
+            pages = table[row[i], js // bs].long()
+            assert (pages >= 0).all(), f"row {i}: a visible key's page was given back"
+            e = cache.keys[pages, js % bs].float()                 # (keys, W)
+            w = torch.softmax((q[i].float() @ e.T) * scale, -1)    # (H, keys)
+            out[i] = (w @ e[:, :value_width]).to(out.dtype)
+
+    def route_by_table(self, token_ids, meta, table, num_experts):
+        ex = table[token_ids.long().clamp(0, table.shape[0] - 1)].long()
+        assert ((ex >= 0) & (ex < num_experts)).all()
+        return ex, meta.seq_row >= 0
+
+    def grouped_linear_glu(self, h, w, route, y, alpha, limit) -> None:
+        ex, live = route
+        I = w.shape[1] // 2
+        wf = w.float()[ex]                                           # (N, top, 2I, K)
+        gu = torch.einsum("ntik,nk->nti", wf, h.float())
+        g, u = gu[..., :I].clamp(max=limit), gu[..., I:].clamp(-limit, limit)
+        act = g * (1.0 / (1.0 + torch.exp(-alpha * g))) * (u + 1)
+        y.copy_(torch.where(live[:, None, None], act, torch.zeros(())).reshape(y.shape).to(y.dtype))
+
+    def grouped_linear_scatter(self, y, w, route, out) -> None:
+        ex, live = route
+        t = torch.einsum("ntdi,nti->ntd", w.float()[ex], y.view(ex.shape[0], ex.shape[1], -1).float())
+        out.copy_(torch.where(live[:, None, None], t, torch.zeros(())).reshape(out.shape))
