@@ -1,0 +1,335 @@
+// Row kernels of the gated parallel block and the latent attention: RMSNorm in groups, short causal convolution with
+// carried state, gated sum of sublayer terms, norm + rotation + paged write of a latent cache entry, rotation of the
+// rotated part of every query head, token-id selection, scaling. One block per token row unless said otherwise. All
+// arithmetic is 32-bit; every sum has an order fixed by the row's own sizes.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// ------------------------------------------------------------------------------------------------ add + grouped RMSNorm
+// As add_rmsnorm (rows == nullptr: x += delta in place; else row selection), with the row split into G equal
+// consecutive parts, each scaled by its own 1 / sqrt(mean(part^2) + eps). Warp w sums the parts w, w + W, ...: a part's
+// sum is a fixed chain per lane followed by the warp's butterfly, whatever else is in the step.
+template <typename TW, typename TH>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_groups_kernel(float* __restrict__ x, const float* __restrict__ delta, const TW* __restrict__ w,
+                          TH* __restrict__ h, const int* __restrict__ rows, int n_src, int D, int G, float eps, int* err) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  const int r = blockIdx.x;
+  int src = r;
+  TH* hr = h + (size_t)r * D;
+  if (rows != nullptr) {
+    src = rows[r];
+    if (src < 0 || src >= n_src) {
+      if (src >= n_src && threadIdx.x == 0) atomicOr(err, FZ_ERR_ROW_RANGE);
+      for (int d = threadIdx.x; d < D; d += blockDim.x) hr[d] = Cvt<TH>::from_f(0.f);
+      return;
+    }
+  }
+  float* xr = x + (size_t)src * D;
+  const float* dr = delta ? delta + (size_t)src * D : nullptr;
+  const bool write_x = rows == nullptr && dr != nullptr;
+  const int Dg = D / G;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, W = blockDim.x >> 5;
+  for (int g = warp; g < G; g += W) {
+    float ss = 0.f;
+    for (int d = g * Dg + lane; d < (g + 1) * Dg; d += 32) {
+      float v = xr[d];
+      if (dr) v += dr[d];
+      if (write_x) xr[d] = v;
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss * (1.0f / (float)Dg) + eps);
+    for (int d = g * Dg + lane; d < (g + 1) * Dg; d += 32) {
+      float v = xr[d];
+      if (dr && !write_x) v += dr[d];
+      hr[d] = Cvt<TH>::from_f(Cvt<TW>::to_f(w[d]) * (v * scale));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ short convolution
+// seg: (first row, rows, first position, state slot) per portion. state: (slots, taps - 1, C) float32, oldest first.
+template <typename T>
+__global__ void __launch_bounds__(256)
+short_conv_kernel(const T* __restrict__ h, const T* __restrict__ w, const float* __restrict__ state,
+                  const int* __restrict__ seg, const int* __restrict__ seq_row, T* __restrict__ out, int C, int taps,
+                  int residual) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  const int n = blockIdx.x;
+  const int s = seq_row[n];
+  T* orow = out + (size_t)n * C;
+  if (s < 0) {
+    for (int c = threadIdx.x; c < C; c += blockDim.x) orow[c] = Cvt<T>::from_f(0.f);
+    return;
+  }
+  const int row0 = seg[4 * s], slot = seg[4 * s + 3];
+  const int i = n - row0;
+  const float* st = state != nullptr && slot >= 0 ? state + (size_t)slot * (taps - 1) * C : nullptr;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int k = i - (taps - 1) + j;
+      float v = 0.f;
+      if (k >= 0) v = Cvt<T>::to_f(h[(size_t)(row0 + k) * C + c]);
+      else if (st != nullptr) v = st[(size_t)(taps - 1 + k) * C + c];
+      acc = fmaf(Cvt<T>::to_f(w[(size_t)c * taps + j]), v, acc);
+    }
+    if (residual) acc += Cvt<T>::to_f(h[(size_t)n * C + c]);
+    orow[c] = Cvt<T>::from_f(acc);
+  }
+}
+
+// After the convolution has read the old state: the state of every portion's request becomes its last taps - 1 inputs
+// (the portion's own rows, and what is left of the old state when the portion is shorter than taps - 1). A thread owns
+// one channel of one portion, reads all it needs and then writes. grid (portions, channel blocks).
+constexpr int MAX_TAPS = 16;
+template <typename T>
+__global__ void __launch_bounds__(256)
+short_conv_state_kernel(const T* __restrict__ h, float* __restrict__ state, const int* __restrict__ seg, int C, int taps) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  const int s = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int row0 = seg[4 * s], cnt = seg[4 * s + 1], slot = seg[4 * s + 3];
+  if (c >= C || cnt <= 0 || slot < 0) return;
+  float* st = state + (size_t)slot * (taps - 1) * C;
+  float keep[MAX_TAPS - 1];
+#pragma unroll
+  for (int m = 0; m < MAX_TAPS - 1; ++m) {
+    if (m < taps - 1) {
+      const int k = cnt - (taps - 1) + m;
+      keep[m] = k >= 0 ? Cvt<T>::to_f(h[(size_t)(row0 + k) * C + c]) : st[(size_t)(taps - 1 + k) * C + c];
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MAX_TAPS - 1; ++m)
+    if (m < taps - 1) st[(size_t)m * C + c] = keep[m];
+}
+
+// ------------------------------------------------------------------------------------------------ gated sum
+// out = a * sigmoid(ga) + (fw * sum_k f[n * terms + k]) * sigmoid(gf); a null gate counts as 1, f null as no term.
+__global__ void gated_sum_kernel(const float* __restrict__ a, const float* __restrict__ ga, const float* __restrict__ f,
+                                 const float* __restrict__ gf, float* __restrict__ out, int N, int D, int terms, float fw) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  const size_t total = (size_t)N * D;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t n = e / D, d = e - n * D;
+    float y = a[e];
+    if (ga) y *= sigmoidf_(ga[e]);
+    if (f) {
+      float t = 0.f;
+      for (int k = 0; k < terms; ++k) t += f[(n * terms + k) * D + d];
+      t *= fw;
+      if (gf) t *= sigmoidf_(gf[e]);
+      y += t;
+    }
+    out[e] = y;
+  }
+}
+
+__global__ void scale_kernel(float* __restrict__ x, float factor, size_t total) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x)
+    x[e] = x[e] * factor;
+}
+
+__global__ void select_tokens_kernel(const int* __restrict__ tokens, const int* __restrict__ src,
+                                     const int* __restrict__ prev_ids, int* __restrict__ out, int N) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n < N) out[n] = src[n] >= 0 ? prev_ids[src[n]] : tokens[n];
+}
+
+// ------------------------------------------------------------------------------------------------ latent cache entry
+// down: (N, L + R) float32. The row's cache entry = [w * down[:L] / rms(down[:L]) | turn(down[L:])], rounded once, stored
+// at the row's place in its pages. pool: (pages, page_size, L + R).
+template <typename TW, typename T>
+__global__ void __launch_bounds__(256)
+latent_cache_write_kernel(const float* __restrict__ down, const TW* __restrict__ w, float eps,
+                          const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rotated,
+                          const int* __restrict__ pos, const int* __restrict__ seq_row, const int* __restrict__ table,
+                          int mb, T* __restrict__ pool, long long page_stride, int page_size, int L, int R, int max_len,
+                          int num_pages, int* err) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  __shared__ float scratch[32];
+  const int n = blockIdx.x;
+  const int row = seq_row[n];
+  if (row < 0) return;
+  const int p = pos[n];
+  if (p < 0 || p >= max_len) {
+    if (threadIdx.x == 0) atomicOr(err, FZ_ERR_POS_RANGE);
+    return;
+  }
+  const int page = table[(size_t)row * mb + p / page_size];
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicOr(err, FZ_ERR_NO_PAGE);
+    return;
+  }
+  const float* in = down + (size_t)n * (L + R);
+  T* e = pool + (size_t)page * page_stride + (size_t)(p % page_size) * (L + R);
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < L; d += blockDim.x) ss = fmaf(in[d], in[d], ss);
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss * (1.0f / (float)L) + eps);
+  for (int d = threadIdx.x; d < L; d += blockDim.x) e[d] = Cvt<T>::from_f(Cvt<TW>::to_f(w[d]) * (in[d] * scale));
+  const int half = rotated >> 1;
+  const float* cr = cos_t + (size_t)p * half;
+  const float* sr = sin_t + (size_t)p * half;
+  for (int d = threadIdx.x; d < R; d += blockDim.x) {
+    float v = in[L + d];
+    if (d < half) {
+      float o1, o2;
+      fz_rope_pair(v, in[L + d + half], cr[d], sr[d], o1, o2);
+      v = o1;
+    } else if (d < rotated) {
+      float o1, o2;
+      fz_rope_pair(in[L + d - half], v, cr[d - half], sr[d - half], o1, o2);
+      v = o2;
+    }
+    e[L + d] = Cvt<T>::from_f(v);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ rotation of heads
+// q: (N, H, W); out[n, h, out_off + d] = turn(q[n, h, off + d]) for d < W - off. grid (N), threads over (h, d).
+template <typename T>
+__global__ void __launch_bounds__(256)
+rotate_heads_kernel(const T* __restrict__ q, int W, int off, const float* __restrict__ cos_t,
+                    const float* __restrict__ sin_t, int rotated, const int* __restrict__ pos,
+                    const int* __restrict__ seq_row, T* __restrict__ out, int Wo, int out_off, int H, int max_len, int* err) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  const int n = blockIdx.x;
+  const int R = W - off, half = rotated >> 1;
+  const int p = pos[n];
+  const bool live = seq_row[n] >= 0 && p >= 0 && p < max_len;
+  if (seq_row[n] >= 0 && !live && threadIdx.x == 0) atomicOr(err, FZ_ERR_POS_RANGE);
+  const float* cr = cos_t + (size_t)(live ? p : 0) * half;
+  const float* sr = sin_t + (size_t)(live ? p : 0) * half;
+  for (int e = threadIdx.x; e < H * R; e += blockDim.x) {
+    const int hh = e / R, d = e - hh * R;
+    const T* in = q + ((size_t)n * H + hh) * W + off;
+    float v = 0.f;
+    if (live) {
+      v = Cvt<T>::to_f(in[d]);
+      if (d < half) {
+        float o1, o2;
+        fz_rope_pair(v, Cvt<T>::to_f(in[d + half]), cr[d], sr[d], o1, o2);
+        v = o1;
+      } else if (d < rotated) {
+        float o1, o2;
+        fz_rope_pair(Cvt<T>::to_f(in[d - half]), v, cr[d - half], sr[d - half], o1, o2);
+        v = o2;
+      }
+    }
+    out[((size_t)n * H + hh) * Wo + out_off + d] = Cvt<T>::from_f(v);
+  }
+}
+}  // namespace
+
+FZ_API int fz_add_rmsnorm_groups(float* x, const float* delta, const void* w, int w_dtype, void* h, int h_dtype,
+                                 const int* rows, int n_out, int n_src, int D, int G, float eps, int* err,
+                                 cudaStream_t stream) {
+  if (n_out <= 0) return FZ_OK;
+  if (G <= 0 || D % G) return FZ_BAD_SHAPE;
+  const int threads = G >= 8 ? 256 : 32 * G;
+#define FZ_GN(TW, TH) do { fz_launch(add_rmsnorm_groups_kernel<TW, TH>, dim3(n_out), dim3(threads), 0, stream, x, delta, \
+    (const TW*)w, (TH*)h, rows, n_src, D, G, eps, err); FZ_LAUNCH_CHECK(); return FZ_OK; } while (0)
+  if (w_dtype == FZ_F32 && h_dtype == FZ_F32) FZ_GN(float, float);
+  if (w_dtype == FZ_F32 && h_dtype == FZ_BF16) FZ_GN(float, __nv_bfloat16);
+  if (w_dtype == FZ_BF16 && h_dtype == FZ_BF16) FZ_GN(__nv_bfloat16, __nv_bfloat16);
+  if (w_dtype == FZ_BF16 && h_dtype == FZ_F32) FZ_GN(__nv_bfloat16, float);
+#undef FZ_GN
+  return FZ_BAD_DTYPE;
+}
+
+FZ_API int fz_short_conv(const void* h, const void* w, float* state, const int* seg, const int* seq_row, void* out,
+                         int dtype, int N, int n_seg, int C, int taps, int residual, cudaStream_t stream) {
+  if (N <= 0) return FZ_OK;
+  if (taps < 1 || taps > MAX_TAPS) return FZ_BAD_SHAPE;
+  if (dtype == FZ_F32) {
+    fz_launch(short_conv_kernel<float>, dim3(N), dim3(256), 0, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual);
+    FZ_LAUNCH_CHECK();
+    if (taps > 1 && state != nullptr && n_seg > 0)
+      fz_launch(short_conv_state_kernel<float>, dim3(n_seg, (C + 255) / 256), dim3(256), 0, stream, (const float*)h, state, seg, C, taps);
+  } else if (dtype == FZ_BF16) {
+    fz_launch(short_conv_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual);
+    FZ_LAUNCH_CHECK();
+    if (taps > 1 && state != nullptr && n_seg > 0)
+      fz_launch(short_conv_state_kernel<__nv_bfloat16>, dim3(n_seg, (C + 255) / 256), dim3(256), 0, stream, (const __nv_bfloat16*)h, state, seg, C, taps);
+  } else {
+    return FZ_BAD_DTYPE;
+  }
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+FZ_API int fz_gated_sum(const float* a, const float* ga, const float* f, const float* gf, float* out, int N, int D,
+                        int terms, float fw, cudaStream_t stream) {
+  if (N <= 0) return FZ_OK;
+  const size_t total = (size_t)N * D;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  fz_launch(gated_sum_kernel, dim3(blocks), dim3(256), 0, stream, a, ga, f, gf, out, N, D, terms, fw);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+FZ_API int fz_scale(float* x, float factor, long long total, cudaStream_t stream) {
+  if (total <= 0) return FZ_OK;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  fz_launch(scale_kernel, dim3(blocks), dim3(256), 0, stream, x, factor, (size_t)total);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+FZ_API int fz_select_tokens(const int* tokens, const int* src, const int* prev_ids, int* out, int N, cudaStream_t stream) {
+  if (N <= 0) return FZ_OK;
+  fz_launch(select_tokens_kernel, dim3((N + 255) / 256), dim3(256), 0, stream, tokens, src, prev_ids, out, N);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+FZ_API int fz_latent_cache_write(const float* down, const void* w, int w_dtype, float eps, const float* cos_t,
+                                 const float* sin_t, int rotated, const int* pos, const int* seq_row, const int* table,
+                                 int mb, void* pool, int dtype, long long page_stride, int page_size, int N, int L, int R,
+                                 int max_len, int num_pages, int* err, cudaStream_t stream) {
+  if (N <= 0) return FZ_OK;
+  if (rotated < 0 || rotated > R || rotated % 2) return FZ_BAD_SHAPE;
+#define FZ_LW(TW, T) do { fz_launch(latent_cache_write_kernel<TW, T>, dim3(N), dim3(128), 0, stream, down, (const TW*)w, eps, \
+    cos_t, sin_t, rotated, pos, seq_row, table, mb, (T*)pool, page_stride, page_size, L, R, max_len, num_pages, err); \
+    FZ_LAUNCH_CHECK(); return FZ_OK; } while (0)
+  if (w_dtype == FZ_F32 && dtype == FZ_F32) FZ_LW(float, float);
+  if (w_dtype == FZ_F32 && dtype == FZ_BF16) FZ_LW(float, __nv_bfloat16);
+  if (w_dtype == FZ_BF16 && dtype == FZ_BF16) FZ_LW(__nv_bfloat16, __nv_bfloat16);
+#undef FZ_LW
+  return FZ_BAD_DTYPE;
+}
+
+FZ_API int fz_rotate_heads(const void* q, int W, int off, const float* cos_t, const float* sin_t, int rotated,
+                           const int* pos, const int* seq_row, void* out, int Wo, int out_off, int dtype, int N, int H,
+                           int max_len, int* err, cudaStream_t stream) {
+  if (N <= 0) return FZ_OK;
+  if (rotated < 0 || rotated > W - off || rotated % 2) return FZ_BAD_SHAPE;
+  if (dtype == FZ_F32)
+    fz_launch(rotate_heads_kernel<float>, dim3(N), dim3(256), 0, stream, (const float*)q, W, off, cos_t, sin_t, rotated, pos, seq_row, (float*)out, Wo, out_off, H, max_len, err);
+  else if (dtype == FZ_BF16)
+    fz_launch(rotate_heads_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, (const __nv_bfloat16*)q, W, off, cos_t, sin_t, rotated, pos, seq_row, (__nv_bfloat16*)out, Wo, out_off, H, max_len, err);
+  else
+    return FZ_BAD_DTYPE;
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+#ifdef FZ_TIMELINE
+FZ_TIMELINE_READER(mix_rows)
+#endif

@@ -23,7 +23,12 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 NVCC_FLAGS += os.environ.get("FZB200_NVCC_EXTRA", "").split()      # extra compiler flags (instrumented builds)
 LIBRARIES: dict[str, list[str]] = {
     "fzb200_core": ["rowwise.cu", "gemm_simt.cu", "attn_simt.cu"],
-    "fzb200_tc": ["gemm_tc.cu", "attn_decode.cu", "attn_prefill.cu", "attn_prefill_tc.cu"],          # bfloat16 only: tcgen05 / TMA kernels
+    # the gated parallel block, attention over a shared latent cache, products per head and per expert (both dtypes)
+    "fzb200_mix": ["mix_rows.cu", "grouped_gemm.cu", "attn_latent.cu"],
+    "fzb200_tc": ["gemm_tc.cu"],                                             # bfloat16 only: tcgen05 / TMA products
+    # bfloat16 only: attention over separate keys and values per kv head (tcgen05 / TMA / mma.sync); built when a model
+    # with such a mixer asks for it
+    "fzb200_attn_tc": ["attn_decode.cu", "attn_prefill.cu", "attn_prefill_tc.cu"],
 }
 _HEADERS = ["common.cuh", "attn_mma.cuh", "tma.cuh", "umma.cuh"]
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -120,6 +120,7 @@ class CudaOps(Ops):
         if self.dtype == torch.bfloat16:
             self.tc = load("fzb200_tc")      # tcgen05 / TMA kernels
         self.use_tensor_cores = self.tc is not None
+        self._attn_tc = self._mix = None   # libraries loaded (and built) when a part first asks for their kernels
         self.prefill_tcgen05 = True        # False: long portions on the mma.sync flash-attention kernel
         self.fuse_swiglu = True            # gate/up product and SwiGLU in one kernel where the sizes allow it
         self.fuse_argmax = True            # lm_head product and argmax in one pass where no logits are asked for
@@ -132,6 +133,20 @@ class CudaOps(Ops):
         self._sms = torch.cuda.get_device_properties(self.device).multi_processor_count
 
     # ---- plumbing
+    @property
+    def attn_tc(self):
+        """The tensor-core attention kernels over separate keys and values (bfloat16)."""
+        if self._attn_tc is None:
+            self._attn_tc = load("fzb200_attn_tc")
+        return self._attn_tc
+
+    @property
+    def mix(self):
+        """The kernels of the gated parallel block, the latent attention and the products per head and per expert."""
+        if self._mix is None:
+            self._mix = load("fzb200_mix")
+        return self._mix
+
     def begin_step(self) -> None:
         """Called by the step function before it launches anything: the kernels of the step all go to the stream that
         is current now (asked for once; it changes when a graph is captured or a caller switches streams)."""
@@ -244,6 +259,8 @@ class CudaOps(Ops):
             raise ValueError(f"attention sizes not supported: {num_heads} heads, {num_kv_heads} kv heads, head_dim "
                              f"{head_dim} (need heads % kv_heads == 0 and head_dim <= 512)")
         # (the prompt kernel takes two heads of a kv head per block at head size 128, else one)
+        if self.use_tensor_cores:
+            self.attn_tc      # built and loaded with the model, not at its first step
         items = num_kv_heads * ((num_heads // num_kv_heads + 1) // 2) if head_dim == 128 else num_heads
         self._attn_heads = min(self._attn_heads or num_heads, num_heads)
         self._attn_items = min(self._attn_items or items, items)
@@ -264,7 +281,7 @@ class CudaOps(Ops):
                                        c_int(table.shape[0]), c_float(scale), _p(self.err), self._stream()), "embed",
                     n * d * (table.element_size() + 4))
 
-    def add_rmsnorm(self, x, delta, weight, eps, h, rows=None) -> None:
+    def add_rmsnorm(self, x, delta, weight, eps, h, rows=None, groups: int = 1) -> None:
         self._want(x, "x", (torch.float32,), 2)
         self._want(weight, "norm weight", (torch.float32, torch.bfloat16), 1)
         self._want(h, "h", (torch.float32, torch.bfloat16), 2)
@@ -279,6 +296,15 @@ class CudaOps(Ops):
             n_out = rows.shape[0]
         if h.shape != (n_out, d) or weight.shape[0] != d:
             raise KernelError(f"add_rmsnorm: h {tuple(h.shape)}, expected {(n_out, d)}; weight {tuple(weight.shape)}")
+        nbytes = n_out * d * (4 + (8 if delta is not None and rows is None else 4 if delta is not None else 0) + h.element_size())
+        if groups != 1:
+            if groups <= 0 or d % groups:
+                raise KernelError(f"add_rmsnorm: a row of {d} values does not split into {groups} equal groups")
+            self._check(self.mix.fz_add_rmsnorm_groups(_p(x), _p(delta), _p(weight), c_int(_CODE[weight.dtype]), _p(h),
+                                                       c_int(_CODE[h.dtype]), _p(rows), c_int(n_out), c_int(n_src), c_int(d),
+                                                       c_int(groups), c_float(eps), _p(self.err), self._stream()),
+                        "add_rmsnorm (groups)", nbytes)
+            return
         self._check(self.core.fz_add_rmsnorm(_p(x), _p(delta), _p(weight), c_int(_CODE[weight.dtype]), _p(h),
                                              c_int(_CODE[h.dtype]), _p(rows), c_int(n_out), c_int(n_src), c_int(d),
                                              c_float(eps), _p(self.err), self._stream()), "add_rmsnorm",
@@ -430,17 +456,17 @@ class CudaOps(Ops):
             key_bytes = hkv * hd * 2 * k.element_size()
             kv = contexts([sg for sg in segs if sg.n < LONG_PORTION]) * key_bytes + 2 * n * hq * hd * q.element_size()
             kv_tiles = sum(sg.pos0 + sg.n for sg in segs if sg.n >= LONG_PORTION) * key_bytes
-        if self.use_tensor_cores and self.tc.fz_attn_decode_check(c_int(hq), c_int(hkv), c_int(hd)) == 0:
+        if self.use_tensor_cores and self.attn_tc.fz_attn_decode_check(c_int(hq), c_int(hkv), c_int(hd)) == 0:
             plan = meta.plan
             if plan is None:
                 raise KernelError("paged_attention: the step was not planned (plan_step with the need 'attention')")
             if plan.n_short_rows > 0:
                 # rows of short portions and decoded tokens: split over key partitions, partials in float32 scratch
-                parts = self.tc.fz_attn_partitions(c_int(meta.max_context))
+                parts = self.attn_tc.fz_attn_partitions(c_int(meta.max_context))
                 need = n * hq * parts * (hd + 2)
                 part_o = self._scratch("attention partials", need, torch.float32)
                 part_ml = part_o[n * hq * parts * hd:]
-                self._check(self.tc.fz_attn_decode(
+                self._check(self.attn_tc.fz_attn_decode(
                     _p(q), _p(k), _p(v), _p(meta.pos), _p(meta.seq_row), _p(meta.seg), _p(table), c_int(table.shape[1]),
                     c_longlong(page_stride), c_int(cache.page_size), _p(out), _p(part_o), _p(part_ml), c_int(n),
                     c_int(hq), c_int(hkv), c_int(hd), c_float(scale), c_int(window), c_int(meta.max_context),
@@ -448,7 +474,7 @@ class CudaOps(Ops):
                     "paged_attention (decode)", kv)
                 self.launches += 1    # the combine kernel
             if plan.n_tiles > 0 and self.prefill_tcgen05 and \
-                    self.tc.fz_attn_prefill_tc_check(c_int(hq), c_int(hkv), c_int(hd), c_int(cache.page_size)) == 0:
+                    self.attn_tc.fz_attn_prefill_tc_check(c_int(hq), c_int(hkv), c_int(hd), c_int(cache.page_size)) == 0:
                 # rows of long portions on the tcgen05 flash-attention kernel; the pieces of tiles that the plan cut along
                 # the keys leave partial results in float32 scratch (a slot per piece and head), merged by a second kernel
                 piece_o = piece_ml = None
@@ -456,7 +482,7 @@ class CudaOps(Ops):
                     rows = plan.n_pieces * hq * TILE_ROWS
                     piece_o = self._scratch("prefill pieces", rows * (hd + 2), torch.float32)
                     piece_ml = piece_o[rows * hd:]
-                self._check(self.tc.fz_attn_prefill_tc(
+                self._check(self.attn_tc.fz_attn_prefill_tc(
                     _p(q), c_int(n), _p(k), _p(v), c_longlong(page_stride), c_int(k.shape[0]), _p(meta.seg), _p(plan.tiles),
                     c_int(plan.n_tiles), _p(plan.cuts), c_int(plan.n_cuts), _p(piece_o), _p(piece_ml), _p(table),
                     c_int(table.shape[1]), c_int(cache.page_size), _p(out), c_int(hq),
@@ -467,7 +493,7 @@ class CudaOps(Ops):
             elif plan.n_tiles > 0 and plan.n_cuts > 0:
                 raise KernelError("paged_attention: the step's tiles are cut along the keys, which only the tcgen05 kernel takes")
             elif plan.n_tiles > 0:
-                self._check(self.tc.fz_attn_prefill(
+                self._check(self.attn_tc.fz_attn_prefill(
                     _p(q), _p(k), _p(v), _p(meta.seg), _p(plan.tiles), c_int(plan.n_tiles), _p(table),
                     c_int(table.shape[1]), c_longlong(page_stride), c_int(cache.page_size), _p(out), c_int(hq),
                     c_int(hkv), c_int(hd), c_float(scale), c_int(window), self._stream()), "paged_attention (prefill)")
@@ -524,3 +550,171 @@ class CudaOps(Ops):
         weights = self._scratch("sampling weights", r * v, torch.float64)       # exp(x / T - max) of every token
         self._check(self.core.fz_sample_filtered(_p(logits), _p(temperature), _p(top_k), _p(top_p), _p(uniform), _p(weights),
                                                  _p(out), c_int(r), c_int(v), self._stream()), "sample_filtered")
+
+    # ---- the gated parallel block
+    def select_tokens(self, tokens, src, prev_ids, out) -> None:
+        for t, name in ((tokens, "tokens"), (src, "src"), (prev_ids, "prev_ids"), (out, "token ids")):
+            self._want(t, name, (torch.int32,), 1)
+        n = tokens.shape[0]
+        if src.shape[0] != n or out.shape[0] != n:
+            raise KernelError("select_tokens: row counts differ")
+        self._check(self.mix.fz_select_tokens(_p(tokens), _p(src), _p(prev_ids), _p(out), c_int(n), self._stream()), "select_tokens")
+
+    def short_conv(self, h, w, state, meta, out, residual: bool = True) -> None:
+        self._want(h, "convolution input", (self.dtype,), 2)
+        self._want(w, "convolution weight", (self.dtype,), 2)
+        self._want(out, "convolution output", (self.dtype,), 2)
+        n, c = h.shape
+        taps = w.shape[1]
+        if w.shape[0] != c or out.shape != h.shape:
+            raise KernelError(f"short_conv: h {tuple(h.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        if taps > 1:
+            if state is None:
+                raise KernelError("short_conv: a convolution of more than one tap needs its state")
+            self._want(state, "convolution state", (torch.float32,), 3)
+            if tuple(state.shape[1:]) != (taps - 1, c):
+                raise KernelError(f"short_conv: state {tuple(state.shape)}, expected (slots, {taps - 1}, {c})")
+        self._check(self.mix.fz_short_conv(_p(h), _p(w), _p(state), _p(meta.seg), _p(meta.seq_row), _p(out),
+                                           c_int(_CODE[self.dtype]), c_int(n), c_int(meta.n_segments), c_int(c), c_int(taps),
+                                           c_int(1 if residual else 0), self._stream()), "short_conv",
+                    n * c * 2 * h.element_size())
+        if taps > 1:
+            self.launches += 1    # the state update
+
+    def gated_sum(self, a, gate_a, f, gate_f, out, f_terms: int = 1, f_weight: float = 1.0) -> None:
+        n, d = a.shape
+        for t, name, rows in ((a, "a", n), (gate_a, "gate_a", n), (f, "f", n * f_terms), (gate_f, "gate_f", n), (out, "out", n)):
+            if t is not None:
+                self._want(t, name, (torch.float32,), 2)
+                if tuple(t.shape) != (rows, d):
+                    raise KernelError(f"gated_sum: {name} {tuple(t.shape)}, expected {(rows, d)}")
+        self._check(self.mix.fz_gated_sum(_p(a), _p(gate_a), _p(f), _p(gate_f), _p(out), c_int(n), c_int(d), c_int(f_terms),
+                                          c_float(f_weight), self._stream()), "gated_sum",
+                    n * d * 4 * (2 + (gate_a is not None) + (gate_f is not None) + (f_terms if f is not None else 0)))
+
+    def scale_(self, x, factor: float) -> None:
+        self._want(x, "x", (torch.float32,))
+        self._check(self.mix.fz_scale(_p(x), c_float(factor), c_longlong(x.numel()), self._stream()), "scale")
+
+    # ---- latent attention
+    def check_latent_attention(self, num_heads: int, key_width: int, value_width: int) -> None:
+        if self.mix.fz_attn_latent_check(c_int(num_heads), c_int(key_width), c_int(value_width)) != 0:
+            raise ValueError(f"latent attention sizes not supported: {num_heads} heads, cached vectors of {key_width} "
+                             f"values of which {value_width} are read as values (need value <= key <= 1024, value <= 512)")
+
+    def _latent_pool(self, cache, width: int):
+        pool = cache.keys
+        if not pool.is_cuda or pool.dtype != self.dtype:
+            raise KernelError(f"latent pool: device {pool.device}, dtype {pool.dtype}; expected CUDA {self.dtype}")
+        if pool.dim() != 3 or pool.shape[1] != cache.page_size or pool.shape[2] != width or pool.stride(2) != 1 \
+                or pool.stride(1) != width:
+            raise KernelError(f"latent pool has shape {tuple(pool.shape)} and strides {pool.stride()}, expected "
+                              f"(pages, {cache.page_size}, {width}) with contiguous pages")
+        return pool, pool.stride(0)
+
+    def latent_cache_write(self, down, norm_weight, eps, cos, sin, rotated, meta, cache) -> None:
+        self._want(down, "latent projection", (torch.float32,), 2)
+        self._want(norm_weight, "latent norm weight", (torch.float32, torch.bfloat16), 1)
+        self._want(cos, "cos table", (torch.float32,), 2)
+        self._want(sin, "sin table", (torch.float32,), 2)
+        n, width = down.shape
+        lat = norm_weight.shape[0]
+        rot = width - lat
+        if rot < 0 or rotated > rot or rotated % 2 or cos.shape[1] != rotated // 2 or sin.shape != cos.shape:
+            raise KernelError(f"latent_cache_write: down {tuple(down.shape)}, latent {lat}, rotated {rotated}, cos {tuple(cos.shape)}")
+        pool, page_stride = self._latent_pool(cache, width)
+        table = meta.table(cache.group)
+        self._check(self.mix.fz_latent_cache_write(
+            _p(down), _p(norm_weight), c_int(_CODE[norm_weight.dtype]), c_float(eps), _p(cos), _p(sin), c_int(rotated),
+            _p(meta.pos), _p(meta.seq_row), _p(table), c_int(table.shape[1]), _p(pool), c_int(_CODE[self.dtype]),
+            c_longlong(page_stride), c_int(cache.page_size), c_int(n), c_int(lat), c_int(rot), c_int(cos.shape[0]),
+            c_int(pool.shape[0]), _p(self.err), self._stream()), "latent_cache_write", n * width * (4 + pool.element_size()))
+
+    def rotate_heads(self, q, offset, cos, sin, rotated, meta, out, out_offset) -> None:
+        self._want(q, "q", (self.dtype,), 3)
+        self._want(out, "rotated q", (self.dtype,), 3)
+        self._want(cos, "cos table", (torch.float32,), 2)
+        self._want(sin, "sin table", (torch.float32,), 2)
+        n, heads, w = q.shape
+        if out.shape[:2] != q.shape[:2] or out_offset + w - offset > out.shape[2] or cos.shape[1] != rotated // 2 \
+                or sin.shape != cos.shape or rotated > w - offset:
+            raise KernelError(f"rotate_heads: q {tuple(q.shape)} from {offset}, out {tuple(out.shape)} at {out_offset}, rotated {rotated}")
+        self._check(self.mix.fz_rotate_heads(_p(q), c_int(w), c_int(offset), _p(cos), _p(sin), c_int(rotated), _p(meta.pos),
+                                             _p(meta.seq_row), _p(out), c_int(out.shape[2]), c_int(out_offset),
+                                             c_int(_CODE[self.dtype]), c_int(n), c_int(heads), c_int(cos.shape[0]),
+                                             _p(self.err), self._stream()), "rotate_heads")
+
+    def linear_heads(self, a, a_offset, k, w, out, out_offset) -> None:
+        self._want(a, "per-head input", (self.dtype,), 3)
+        self._want(w, "per-head weight", (self.dtype,), 3)
+        self._want(out, "per-head output", (self.dtype,), 3)
+        n, heads, wa = a.shape
+        m = w.shape[1]
+        if w.shape[0] != heads or w.shape[2] != k or a_offset + k > wa or out.shape[:2] != a.shape[:2] \
+                or out_offset + m > out.shape[2]:
+            raise KernelError(f"linear_heads: a {tuple(a.shape)} from {a_offset}, w {tuple(w.shape)}, out {tuple(out.shape)} at {out_offset}")
+        es = a.element_size()
+        self._check(self.mix.fz_linear_heads(
+            c_void_p(a.data_ptr() + a_offset * es), c_longlong(heads * wa), c_longlong(wa), _p(w),
+            c_void_p(out.data_ptr() + out_offset * es), c_longlong(heads * out.shape[2]), c_longlong(out.shape[2]),
+            c_int(_CODE[self.dtype]), c_int(_CODE[self.dtype]), c_int(n), c_int(heads), c_int(m), c_int(k), self._stream()),
+            "linear_heads", (n * heads * (k + m) + heads * m * k) * es)
+
+    def latent_attention(self, q, cache, meta, out, value_width, scale, window) -> None:
+        self._want(q, "q", (self.dtype,), 3)
+        self._want(out, "attention output", (self.dtype,), 3)
+        n, heads, width = q.shape
+        if tuple(out.shape) != (n, heads, value_width):
+            raise KernelError(f"latent_attention: q {tuple(q.shape)}, out {tuple(out.shape)}, values {value_width}")
+        pool, page_stride = self._latent_pool(cache, width)
+        table = meta.table(cache.group)
+        nbytes = 0
+        if self._profile is not None:
+            nbytes = contexts(list(getattr(meta, "segments", ()))) * width * pool.element_size() + n * heads * (width + value_width) * q.element_size()
+        self._check(self.mix.fz_attn_latent(
+            _p(q), _p(pool), _p(meta.pos), _p(meta.seq_row), _p(table), c_int(table.shape[1]), c_longlong(page_stride),
+            c_int(cache.page_size), c_int(pool.shape[0]), _p(out), c_int(_CODE[self.dtype]), c_int(n), c_int(heads),
+            c_int(width), c_int(value_width), c_float(scale), c_int(window), _p(self.err), self._stream()),
+            "latent_attention", nbytes)
+
+    # ---- experts chosen by a table
+    def route_by_table(self, token_ids, meta, table, num_experts):
+        self._want(token_ids, "token ids", (torch.int32,), 1)
+        self._want(table, "expert table", (torch.int32,), 2)
+        n, top = token_ids.shape[0], table.shape[1]
+        tile = int(self.mix.fz_grouped_tile_rows())
+        max_tiles = -(-n * top // tile) + min(num_experts, n * top)
+        idx = self._scratch("expert route", 2 * n * top + 3 * max_tiles, torch.int32)
+        a_idx, c_idx, tiles = idx[:n * top], idx[n * top: 2 * n * top], idx[2 * n * top: 2 * n * top + 3 * max_tiles]
+        self._check(self.mix.fz_route_by_table(_p(token_ids), _p(meta.seq_row), _p(table), c_int(n), c_int(table.shape[0]),
+                                               c_int(top), c_int(num_experts), _p(a_idx), _p(c_idx), _p(tiles),
+                                               c_int(max_tiles), _p(self.err), self._stream()), "route_by_table")
+        return (a_idx, c_idx, tiles, max_tiles, n, top, meta.seq_row)
+
+    def grouped_linear_glu(self, h, w, route, y, alpha, limit) -> None:
+        a_idx, c_idx, tiles, max_tiles, n, top, seq_row = route
+        self._want(h, "expert input", (self.dtype,), 2)
+        self._want(w, "expert gate/up weights", (self.dtype,), 3)
+        self._want(y, "expert activation", (self.dtype,), 2)
+        k, inter = h.shape[1], w.shape[1] // 2
+        if h.shape[0] != n or w.shape[2] != k or w.shape[1] != 2 * inter or tuple(y.shape) != (n * top, inter):
+            raise KernelError(f"grouped_linear_glu: h {tuple(h.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+        self._check(self.mix.fz_grouped_linear(_p(h), _p(w), _p(y), _p(tiles), c_int(max_tiles), _p(a_idx), c_void_p(0),
+                                               c_int(_CODE[self.dtype]), c_int(_CODE[self.dtype]), c_int(inter), c_int(k),
+                                               c_int(1), c_float(alpha), c_float(limit), c_void_p(0), c_int(0), c_int(0),
+                                               self._stream()),
+                    "grouped_linear_glu", (min(w.shape[0], n * top) * 2 * inter * k + n * k + n * top * inter) * h.element_size())
+
+    def grouped_linear_scatter(self, y, w, route, out) -> None:
+        a_idx, c_idx, tiles, max_tiles, n, top, seq_row = route
+        self._want(y, "expert activation", (self.dtype,), 2)
+        self._want(w, "expert down weights", (self.dtype,), 3)
+        self._want(out, "expert outputs", (torch.float32,), 2)
+        inter, d = y.shape[1], w.shape[1]
+        if y.shape[0] != n * top or w.shape[2] != inter or tuple(out.shape) != (n * top, d):
+            raise KernelError(f"grouped_linear_scatter: y {tuple(y.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        self._check(self.mix.fz_grouped_linear(_p(y), _p(w), _p(out), _p(tiles), c_int(max_tiles), c_void_p(0), _p(c_idx),
+                                               c_int(_CODE[self.dtype]), c_int(_CODE[torch.float32]), c_int(d), c_int(inter),
+                                               c_int(0), c_float(0.0), c_float(0.0), _p(seq_row), c_int(n), c_int(top),
+                                               self._stream()),
+                    "grouped_linear_scatter", min(w.shape[0], n * top) * d * inter * y.element_size() + n * top * (inter * y.element_size() + d * 4))

@@ -1,6 +1,6 @@
 """Trace replay: feeds given token ids through a model step by step and writes the logits. It samples nothing.
 
-    bin/trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N [--page-size P]
+    bin/trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N [--page-size P] [--max-requests R]
     python -m fusezap_core_b200 replay --model DIR ...            (the same)
 
 Steps come on standard input, one JSON object a line:
@@ -9,7 +9,8 @@ All entries of a step run as one batch through the engine's own step function, c
 has no forward pass, cache or loader of its own. For a step that wants logits, `DIR/<step>.f32` receives them as
 little-endian float32 [wanted, vocab], in the order of the entries and of `want`. After every step a line `done <step>`
 is printed and flushed. `end` lists requests whose pages are given back after the step. The pool holds --max-tokens
-tokens (in pages of --page-size, default 16), so pages are reused.
+tokens (in pages of --page-size, default 16) and has state slots and block tables for --max-requests requests
+(default 4), so pages and slots are reused.
 """
 import argparse
 import json
@@ -24,6 +25,7 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True, help="most tokens live requests hold at any time")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--max-requests", type=int, default=4, help="requests live at any time (state slots, block tables)")
     ap.add_argument("--device", default="cuda:0")
     a = ap.parse_args(argv)
 
@@ -37,9 +39,9 @@ def main(argv=None) -> int:
     num_pages = -(-a.max_tokens // ps)
     max_len = num_pages * ps
     model = load_model(a.model, a.dtype, a.device, max_len=max_len)
-    cache = CacheManager(model.cache_needs(), model.state_needs(), ps, num_pages, max_requests=64,
+    cache = CacheManager(model.cache_needs(), model.state_needs(), ps, num_pages, max_requests=a.max_requests,
                          max_model_len=max_len, dtype=model.ops.dtype, device=model.device)
-    runner = StepRunner(model, cache, max_rows=max_len, max_wanted=max_len, max_segments=64)
+    runner = StepRunner(model, cache, max_rows=max_len, max_wanted=max_len, max_segments=a.max_requests)
     runner.ws.row_capacity = min(max_len, 512)
     for line in sys.stdin:
         line = line.strip()

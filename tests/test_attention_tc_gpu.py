@@ -16,8 +16,8 @@ def run_both(Hq, Hkv, hd, bs, window, lengths, rows, seed=0, prefill_mode=0):
     kernel takes the long portions (0: chosen by shape, 1: one head per block, 2: two heads per block)."""
     from fusezap_core_b200.kernels import cuda_ops
     cu, pl = cuda_ops("bfloat16"), PlainOps(BF)
-    assert cu.use_tensor_cores and cu.tc.fz_attn_decode_check(Hq, Hkv, hd) == 0
-    assert cu.tc.fz_attn_prefill_tc_mode(prefill_mode) == 0
+    assert cu.use_tensor_cores and cu.attn_tc.fz_attn_decode_check(Hq, Hkv, hd) == 0
+    assert cu.attn_tc.fz_attn_prefill_tc_mode(prefill_mode) == 0
     g = torch.Generator().manual_seed(seed + Hq + hd + window)
     mb = -(-max(lengths) // bs)
     pages = mb * len(lengths) + 3
@@ -40,7 +40,7 @@ def run_both(Hq, Hkv, hd, bs, window, lengths, rows, seed=0, prefill_mode=0):
     try:
         cu.paged_attention(q.cuda(), cc, meta, o, Hq, Hkv, hd, scale, window)
     finally:
-        cu.tc.fz_attn_prefill_tc_mode(0)
+        cu.attn_tc.fz_attn_prefill_tc_mode(0)
     pl.paged_attention(q, cp, Meta(pos, seq_row, table, "cpu"), op, Hq, Hkv, hd, scale, window)
     cu.check_errors()
     run_both.last_plan = meta.plan
