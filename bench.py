@@ -149,7 +149,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--reference-device", default="CUDA", help="the reference's device name for --impl reference")
-    ap.add_argument("--workload", default="decode", choices=["decode", "stream"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "stream", "pepilix"],
+                    help="pepilix: prefill and decode of the Pepilix design at a few layer sizes, beside the dense decoder "
+                         "at equal width, layers, heads and active feed-forward size")
+    ap.add_argument("--sizes", default="w1024,w2048", help="pepilix workload: which of its sizes to run")
     ap.add_argument("--leave-out", default="", metavar="OPS",
                     help="measurement aid, NOT a benchmark: comma-separated kernel-table operations turned into no-ops "
                          "(e.g. paged_attention, add_rmsnorm, linear_swiglu), to read an operation's cost inside the "
@@ -164,7 +167,7 @@ def main() -> int:
     ap.add_argument("--requests", type=int, default=32, help="stream workload: number of requests")
     ap.add_argument("--new-tokens", type=int, default=256, help="stream workload: tokens generated per request")
     a = ap.parse_args()
-    if a.preset is None and a.workload != "stream":
+    if a.preset is None and a.workload == "decode":
         a.preset = "llama-3.1-8b"
     if a.impl == "reference":
         return reference_arm(a)
@@ -174,6 +177,8 @@ def main() -> int:
     a.warmup = max(a.warmup, 3)
     if a.workload == "stream":
         return stream_workload(a)
+    if a.workload == "pepilix":
+        return pepilix_workload(a)
 
     import numpy as np
     import torch
@@ -384,6 +389,135 @@ def main() -> int:
     if left_out:
         line["invalid"] = "operations left out: " + ", ".join(left_out)
     print(json.dumps(line))
+    return 0
+
+
+# Layer sizes for the Pepilix workload: (width, heads, unrotated, rotated, value, latent, experts, top, expert ff, vocab).
+# The dense decoder beside it has the same width, layers, heads and vocabulary, head size unrotated + rotated rounded
+# to 64 or 128 with a quarter as many kv heads, and an intermediate size of top x expert ff (the same active weights).
+PEPILIX_SIZES = {
+    "w1024": (1024, 8, 64, 64, 64, 256, 16, 2, 1024, 32768),
+    "w2048": (2048, 16, 64, 64, 128, 512, 32, 4, 1024, 32768),
+}
+
+
+def pepilix_workload(a) -> int:
+    """`--workload pepilix`: for each size, a 2,048-token prompt (median of five) and decode steps at --batch requests
+    with contexts near --context, through `LLMEngine.step()`, for Pepilix and for the dense decoder at equal size; then
+    one profiled prompt and decode step of each (kernel by kernel, CUDA events) for the share and GB/s of every kernel
+    class. Random bf16 weights, --layers layers (default 4)."""
+    import numpy as np
+    import torch
+    from fusezap_core_b200 import LLMEngine, SamplingParams
+    from fusezap_core_b200.config import EngineConfig
+    from fusezap_core_b200.engine.model import random_model
+
+    L = a.layers or 4
+    ctx, batch, page, dev = min(a.context, 4096), a.batch, a.page_size, torch.device("cuda:0")
+    pk = peaks()
+    rng = np.random.default_rng(5)
+
+    def configs(name):
+        D, H, dn, dr, dv, r, E, top, ff, V = PEPILIX_SIZES[name]
+        mixer = {"heads": H, "dim": dn, "rot_dim": dr, "vdim": dv, "kv_rank": r, "scale": (dn + dr) ** -0.5,
+                 "rot": {"base": 10000.0, "dims": dr}}
+        mlp = {"kind": "moe", "router": {"experts": E, "top": top}, "expert": {"ff": ff, "limit": 7.0}}
+        pep = {"architecture": "Pepilix", "vocab": V, "width": D, "embedding": {"scale": 1.0}, "logit_scale": 1.0,
+               "norm": {"eps": 1e-6, "groups": 2}, "canon": {"taps": 4},
+               "layers": [{"type": "latent_attention", "mixer": mixer, "mlp": mlp} for _ in range(L)]}
+        hd = 64 if dn + dr <= 64 else 128
+        dense = {"model_type": "llama", "hidden_size": D, "intermediate_size": top * ff, "num_hidden_layers": L,
+                 "num_attention_heads": H, "num_key_value_heads": max(1, H // 4), "head_dim": hd, "vocab_size": V,
+                 "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "max_position_embeddings": ctx, "tie_word_embeddings": True}
+        return pep, dense
+
+    def run(cfg, profile: bool):
+        model = random_model(cfg, "bfloat16", dev, seed=0, max_len=ctx)
+        V = model.spec.vocab_size
+        pages = batch * (-(-ctx // page)) + 8
+        eng = LLMEngine(model, EngineConfig(num_blocks=pages, block_size=page, max_num_seqs=batch, max_prefill_tokens=a.prefill_tokens,
+                                            max_model_len=ctx, prefill_first=1 << 30, profile=profile))
+        out = {"weight_gb": round(model.weight_bytes() / 1e9, 3)}
+        ids = rng.integers(0, V, a.prefill_tokens).tolist()
+        times = []
+        for i in range(2 if profile else 6):
+            rid = eng.add_request(ids, SamplingParams(max_tokens=1, ignore_eos=True))
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            eng.step()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(end))
+            eng.release(rid)
+        if profile:
+            out["prefill_classes"] = eng.profile_report()["classes"]
+            model.ops.start_profile()
+        else:
+            ms = sorted(times[1:])[2]
+            out["prefill"] = {"tokens": a.prefill_tokens, "ms": round(ms, 3), "tok_s": round(a.prefill_tokens * 1000.0 / ms, 1)}
+        steps, warm = (4, 2) if profile else (a.steps, a.warmup)
+        n_prompt = ctx - steps - warm - 4
+        rids = [eng.add_request(rng.integers(0, V, n_prompt).tolist(), SamplingParams(max_tokens=steps + warm + 2, ignore_eos=True))
+                for _ in range(batch)]
+        while any(not eng.requests[r].decoding for r in rids):
+            eng.step()
+        if profile:
+            model.ops.start_profile()
+        for _ in range(warm):
+            eng.step()
+        torch.cuda.synchronize()
+        launches0 = model.ops.launches
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        n_tok = 0
+        for _ in range(steps):
+            n_tok += len(eng.step())
+        end.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end) / steps
+        if profile:
+            out["decode_classes"] = eng.profile_report()["classes"]
+        else:
+            out["decode"] = {"batch": batch, "context": n_prompt + warm + steps // 2, "ms_per_step": round(ms, 4),
+                             "tok_s": round(n_tok * 1000.0 / (ms * steps), 1)}
+            out["launches"] = model.ops.launches - launches0 + steps * max(eng.launches_per_graph.values(), default=0)
+        for r in rids:
+            eng.abort(r)
+        if profile:
+            model.ops._profile = None       # the kernel table is shared by the models of a process
+        del eng, model
+        torch.cuda.empty_cache()
+        return out
+
+    clocks = ClockSampler()
+    clocks.start()
+    sizes, launches = {}, 0
+    for name in [n for n in a.sizes.split(",") if n]:
+        if name not in PEPILIX_SIZES:
+            raise SystemExit(f"--sizes: {name!r} is not one of {sorted(PEPILIX_SIZES)}")
+        pep, dense = configs(name)
+        res = {"pepilix": run(pep, False), "dense": run(dense, False)}
+        launches += res["pepilix"].pop("launches", 0) + res["dense"].pop("launches", 0)
+        if not a.no_points:
+            for which, cfg in (("pepilix", pep), ("dense", dense)):
+                prof = run(cfg, True)
+                for k in ("prefill_classes", "decode_classes"):
+                    res[which][k] = [{"class": c["class"], "launches": c["launches"], "ms": c["ms"], "share": c["share"],
+                                      "of_hbm": None if c["ideal_gbs"] is None else round(c["ideal_gbs"] / pk["hbm_gbs"], 3)}
+                                     for c in prof[k]]
+        sizes[name] = res
+    clk = clocks.stop()
+    first = sizes[next(iter(sizes))]
+    print(json.dumps({
+        "metric": "pepilix_decode_tokens_per_s", "value": first["pepilix"]["decode"]["tok_s"], "unit": "tok/s", "n_gpus": 1,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": first["pepilix"]["decode"]["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {"workload": "pepilix", "layers": L, "global_batch": batch, "seq_len": ctx, "page_size": page,
+                   "sizes": {n: dict(zip(("width", "heads", "dim", "rot_dim", "vdim", "kv_rank", "experts", "top", "ff", "vocab"),
+                                         PEPILIX_SIZES[n])) for n in sizes},
+                   "weights": "random N(0,0.02)", "peaks": pk["source"], "l2": "inputs larger than L2"},
+        "clocks": clk, "gpu_launches": int(launches), "sizes": sizes}))
     return 0
 
 

@@ -103,6 +103,7 @@ class StepMeta:
         self.page_size = 0        # of the cache the step was packed against
         self.max_portion = 0      # the longest portion
         self.plan = None          # whatever the kernel table's `plan_step` keeps about this step (launch sizes and the like)
+        self.latent_extra = 0     # kernel table: how many blocks beyond rows x heads / 64 the latent attention launches
 
     # device views (static addresses; sliced to the step's sizes)
     @property

@@ -120,11 +120,12 @@ class CudaOps(Ops):
         if self.dtype == torch.bfloat16:
             self.tc = load("fzb200_tc")      # tcgen05 / TMA kernels
         self.use_tensor_cores = self.tc is not None
-        self._attn_tc = self._mix = None   # libraries loaded (and built) when a part first asks for their kernels
+        self._attn_tc = self._mix = self._mix_tc = None   # libraries loaded (and built) when a part first asks for their kernels
         self.prefill_tcgen05 = True        # False: long portions on the mma.sync flash-attention kernel
         self.fuse_swiglu = True            # gate/up product and SwiGLU in one kernel where the sizes allow it
         self.fuse_argmax = True            # lm_head product and argmax in one pass where no logits are asked for
         self.fuse_rope = True              # q/k/v product, rotation and cache write in one kernel (few-token steps)
+        self.latent_tensor_cores = True    # latent attention on tensor cores where the sizes allow it (bfloat16)
         self.cut_prefill_keys = True       # few query tiles with many keys behind them are cut along the keys
         self._profile = None               # a StepProfile while the engine profiles its steps
         # the fewest query heads, and the fewest items of a query tile on the prompt kernel, among the attention layers
@@ -133,6 +134,13 @@ class CudaOps(Ops):
         self._sms = torch.cuda.get_device_properties(self.device).multi_processor_count
 
     # ---- plumbing
+    @property
+    def mix_tc(self):
+        """The tensor-core attention over a shared latent cache (bfloat16)."""
+        if self._mix_tc is None:
+            self._mix_tc = load("fzb200_mix_tc")
+        return self._mix_tc
+
     @property
     def attn_tc(self):
         """The tensor-core attention kernels over separate keys and values (bfloat16)."""
@@ -226,6 +234,12 @@ class CudaOps(Ops):
     def plan_step(self, meta, needs: tuple) -> None:
         """Called when a step has been packed on the host, before its one copy to the device: writes the attention
         kernels' tile list into the block's extra part and keeps the launch sizes in `meta.plan`."""
+        if "latent_attention" in needs:
+            # The latent attention takes 64 (row, head) pairs of one portion per block: rows x heads / 64 blocks and at
+            # most one more per portion. A step of single tokens may be replayed as a captured graph with other
+            # requests in its rows, so it allows one per row.
+            single = all(sg.n == 1 for sg in meta.segments)
+            meta.latent_extra = meta.n_rows if single else meta.n_segments
         if "attention" not in needs:
             meta.plan = None
             return
@@ -250,7 +264,8 @@ class CudaOps(Ops):
     def step_signature(self, meta) -> tuple:
         """What, beside the row counts, fixes the kernel launches of a step (two steps that agree in it launch alike)."""
         plan = meta.plan
-        return (plan.n_tiles, plan.n_short_rows > 0, plan.n_cuts, plan.single_tokens) if plan is not None else ()
+        latent = (getattr(meta, "latent_extra", 0),)
+        return (plan.n_tiles, plan.n_short_rows > 0, plan.n_cuts, plan.single_tokens, *latent) if plan is not None else latent
 
     def check_attention(self, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
         if head_dim % 16:
@@ -601,6 +616,8 @@ class CudaOps(Ops):
         if self.mix.fz_attn_latent_check(c_int(num_heads), c_int(key_width), c_int(value_width)) != 0:
             raise ValueError(f"latent attention sizes not supported: {num_heads} heads, cached vectors of {key_width} "
                              f"values of which {value_width} are read as values (need value <= key <= 1024, value <= 512)")
+        if self.use_tensor_cores and self.latent_tensor_cores:
+            self.mix_tc       # built and loaded with the model, not at its first step
 
     def _latent_pool(self, cache, width: int):
         pool = cache.keys
@@ -671,6 +688,16 @@ class CudaOps(Ops):
         nbytes = 0
         if self._profile is not None:
             nbytes = contexts(list(getattr(meta, "segments", ()))) * width * pool.element_size() + n * heads * (width + value_width) * q.element_size()
+        if self.use_tensor_cores and self.latent_tensor_cores and \
+                self.mix_tc.fz_attn_latent_tc_check(c_int(heads), c_int(width), c_int(value_width)) == 0:
+            blocks = n * heads // 64 + max(1, int(getattr(meta, "latent_extra", 0)) or n)
+            self._check(self.mix_tc.fz_attn_latent_tc(
+                _p(q), _p(pool), _p(meta.seq_row), _p(meta.seg), c_int(meta.n_segments), _p(table), c_int(table.shape[1]),
+                c_longlong(page_stride), c_int(cache.page_size), c_int(pool.shape[0]), _p(out), c_int(n), c_int(blocks),
+                c_int(heads), c_int(width), c_int(value_width), c_float(scale), c_int(window), _p(self.err), self._stream()),
+                "latent_attention (tensor cores)", nbytes)
+            self.launches += 1    # the kernel that zeroes rows of padding
+            return
         self._check(self.mix.fz_attn_latent(
             _p(q), _p(pool), _p(meta.pos), _p(meta.seq_row), _p(table), c_int(table.shape[1]), c_longlong(page_stride),
             c_int(cache.page_size), c_int(pool.shape[0]), _p(out), c_int(_CODE[self.dtype]), c_int(n), c_int(heads),

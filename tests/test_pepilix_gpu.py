@@ -180,7 +180,8 @@ def _attention_reference(q, entries, Wv, scale, lo, p):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,W,Wv,page", [(6, 160, 128, 16), (40, 22, 16, 4), (1, 104, 72, 8), (3, 48, 40, 64)])
+@pytest.mark.parametrize("H,W,Wv,page", [(6, 160, 128, 16), (40, 22, 16, 4), (1, 104, 72, 8), (3, 48, 40, 64),
+                                         (16, 576, 512, 16), (5, 64, 32, 8), (20, 96, 80, 4), (70, 32, 32, 16)])
 def test_latent_attention_rows_of_any_portion(dtype, H, W, Wv, page):
     """Two requests on shuffled pages: a long portion behind a prefix, single tokens, and a padding row, against the
     plain softmax over each row's own keys."""
@@ -207,6 +208,14 @@ def test_latent_attention_rows_of_any_portion(dtype, H, W, Wv, page):
         ref = _attention_reference(q[i], ent[s], Wv, 0.3, 0, p)
         assert ((out[i].cpu().to(F) - ref).abs() <= tol * (1 + ref.abs())).all(), f"row {i}"
     assert float(out[46].float().abs().max()) == 0.0
+    if dtype == "bfloat16":       # the general kernel, where the tensor-core one had taken the sizes: the same within rounding
+        ops.latent_tensor_cores = False
+        try:
+            out2 = torch.empty_like(out)
+            ops.latent_attention(q.to(DEV), LayerCache(keys=pool, group=0, page_size=page), meta, out2, Wv, 0.3, 0)
+        finally:
+            ops.latent_tensor_cores = True
+        assert (out2.float() - out.float()).abs().max() <= 2.0 ** -5
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -239,7 +248,7 @@ def test_window_edges(dtype, window):
     """With a window the key at p - window + 1 counts and the one at p - window does not, for portion rows and single
     tokens alike (shown by a key that would dominate if it were seen)."""
     ops, g, dt = cuda_ops(dtype), torch.Generator().manual_seed(window), DT[dtype]
-    H, W, Wv, page, T = 3, 40, 24, 8, 120
+    H, W, Wv, page, T = 3, 48, 24, 8, 120
     ent = (torch.randn(T, W, generator=g) * 0.3).to(dt)
     probe = torch.zeros(W)
     probe[Wv + 1] = 6.0
