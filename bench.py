@@ -413,7 +413,7 @@ def pepilix_workload(a) -> int:
     from fusezap_core_b200.engine.model import random_model
 
     L = a.layers or 4
-    ctx, batch, page, dev = min(a.context, 4096), a.batch, a.page_size, torch.device("cuda:0")
+    ctx, batch, page, dev = max(min(a.context, 4096), a.prefill_tokens + 16), a.batch, a.page_size, torch.device("cuda:0")
     pk = peaks()
     rng = np.random.default_rng(5)
 

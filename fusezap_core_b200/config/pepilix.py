@@ -113,8 +113,8 @@ class PepilixConfig:
             raise ValueError(f"config: vocab, width and the number of layers must be positive")
         if self.norm_groups <= 0 or self.width % self.norm_groups:
             raise ValueError(f"config: width {self.width} does not split into {self.norm_groups} equal norm groups")
-        if self.canon_taps < 1:
-            raise ValueError(f"config: canon.taps must be at least 1, got {self.canon_taps}")
+        if self.canon_taps < 0:
+            raise ValueError(f"config: canon.taps cannot be negative, got {self.canon_taps}")
         if not self.norm_eps > 0:
             raise ValueError(f"config: norm.eps must be positive, got {self.norm_eps!r}")
         for i, L in enumerate(self.layers):
@@ -145,11 +145,12 @@ class PepilixConfig:
             vocab=int(c["vocab"]), width=int(c["width"]),
             embedding_scale=float((c.get("embedding") or {}).get("scale", 1.0)), logit_scale=float(c.get("logit_scale", 1.0)),
             norm_eps=float(c["norm"]["eps"]), norm_groups=int(c["norm"].get("groups", 1)),
-            canon_taps=int((c.get("canon") or {}).get("taps", 1)), layers=tuple(layers),
+            canon_taps=int((c.get("canon") or {}).get("taps", 0)),      # no `canon`: no convolution
+            layers=tuple(layers),
             max_position=int(c.get("max_position", 1 << 17)))
 
     def to_json(self) -> dict:
-        return {"architecture": "Pepilix", "canon": {"taps": self.canon_taps}, "embedding": {"scale": self.embedding_scale},
+        return {"architecture": "Pepilix", **({"canon": {"taps": self.canon_taps}} if self.canon_taps else {}), "embedding": {"scale": self.embedding_scale},
                 "layers": [{"mixer": L.mixer.to_json(), "mlp": L.mlp.to_json() if L.mlp else None, "type": L.type}
                            for L in self.layers],
                 "logit_scale": self.logit_scale, "norm": {"eps": self.norm_eps, "groups": self.norm_groups},

@@ -131,13 +131,13 @@ grouped_gemm_kernel(const GroupedArgs p) {
 }
 
 // One block sorts the step's N * top (row, choice) pairs by expert. Outputs: a_idx[s] = row and c_idx[s] = row * top +
-// choice of the pair at sorted place s; tiles (expert, first place, pairs) for row tiles of BM pairs, the unused ones
+// choice of the pair at sorted place s; tiles (expert, first place, pairs) for row tiles of tile_rows pairs, the unused ones
 // with 0 pairs; rows of padding (seq_row < 0) have no pairs. The order of pairs within an expert is whatever the atomic
 // counters give: no result depends on it.
 __global__ void __launch_bounds__(1024)
 route_by_table_kernel(const int* __restrict__ token_ids, const int* __restrict__ seq_row, const int* __restrict__ table,
                       int N, int V, int top, int E, int* __restrict__ a_idx, int* __restrict__ c_idx,
-                      int* __restrict__ tiles, int max_tiles, int* err) {
+                      int* __restrict__ tiles, int max_tiles, int tile_rows, int* err) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   extern __shared__ int sm[];
@@ -161,10 +161,10 @@ route_by_table_kernel(const int* __restrict__ token_ids, const int* __restrict__
     int at = 0, t = 0;
     for (int e = 0; e < E; ++e) {
       start[e] = at;
-      for (int f = 0; f < count[e] && t < max_tiles; f += BM, ++t) {
+      for (int f = 0; f < count[e] && t < max_tiles; f += tile_rows, ++t) {
         tiles[3 * t] = e;
         tiles[3 * t + 1] = at + f;
-        tiles[3 * t + 2] = min(BM, count[e] - f);
+        tiles[3 * t + 2] = min(tile_rows, count[e] - f);
       }
       at += count[e];
     }
@@ -212,11 +212,12 @@ FZ_API int fz_linear_heads(const void* A, long long lda, long long a_head, const
 }
 
 FZ_API int fz_route_by_table(const int* token_ids, const int* seq_row, const int* table, int N, int V, int top, int E,
-                             int* a_idx, int* c_idx, int* tiles, int max_tiles, int* err, cudaStream_t stream) {
+                             int* a_idx, int* c_idx, int* tiles, int max_tiles, int tile_rows, int* err,
+                             cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
-  if (E <= 0 || E > 4096 || top <= 0) return FZ_BAD_SHAPE;
+  if (E <= 0 || E > 4096 || top <= 0 || tile_rows <= 0 || tile_rows > BM) return FZ_BAD_SHAPE;
   fz_launch(route_by_table_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int), stream, token_ids, seq_row, table, N, V,
-            top, E, a_idx, c_idx, tiles, max_tiles, err);
+            top, E, a_idx, c_idx, tiles, max_tiles, tile_rows, err);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }

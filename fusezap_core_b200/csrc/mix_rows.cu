@@ -88,7 +88,7 @@ short_conv_kernel(const T* __restrict__ h, const T* __restrict__ w, const float*
 // After the convolution has read the old state: the state of every portion's request becomes its last taps - 1 inputs
 // (the portion's own rows, and what is left of the old state when the portion is shorter than taps - 1). A thread owns
 // one channel of one portion, reads all it needs and then writes. grid (portions, channel blocks).
-constexpr int MAX_TAPS = 16;
+constexpr int MAX_TAPS = 32;
 template <typename T>
 __global__ void __launch_bounds__(256)
 short_conv_state_kernel(const T* __restrict__ h, float* __restrict__ state, const int* __restrict__ seg, int C, int taps) {

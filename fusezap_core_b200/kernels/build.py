@@ -25,7 +25,7 @@ LIBRARIES: dict[str, list[str]] = {
     "fzb200_core": ["rowwise.cu", "gemm_simt.cu", "attn_simt.cu"],
     # the gated parallel block, attention over a shared latent cache, products per head and per expert (both dtypes)
     "fzb200_mix": ["mix_rows.cu", "grouped_gemm.cu", "attn_latent.cu"],
-    "fzb200_mix_tc": ["attn_latent_tc.cu"],                                  # bfloat16 only: the same on tensor cores
+    "fzb200_mix_tc": ["attn_latent_tc.cu", "grouped_gemm_tc.cu"],                           # bfloat16 only: the same on tensor cores
     "fzb200_tc": ["gemm_tc.cu"],                                             # bfloat16 only: tcgen05 / TMA products
     # bfloat16 only: attention over separate keys and values per kv head (tcgen05 / TMA / mma.sync); built when a model
     # with such a mixer asks for it

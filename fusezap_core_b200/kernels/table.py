@@ -125,6 +125,7 @@ class CudaOps(Ops):
         self.fuse_swiglu = True            # gate/up product and SwiGLU in one kernel where the sizes allow it
         self.fuse_argmax = True            # lm_head product and argmax in one pass where no logits are asked for
         self.fuse_rope = True              # q/k/v product, rotation and cache write in one kernel (few-token steps)
+        self.grouped_tensor_cores = True   # products per head and per expert on tensor cores where the sizes allow it
         self.latent_tensor_cores = True    # latent attention on tensor cores where the sizes allow it (bfloat16)
         self.cut_prefill_keys = True       # few query tiles with many keys behind them are cut along the keys
         self._profile = None               # a StepProfile while the engine profiles its steps
@@ -671,6 +672,14 @@ class CudaOps(Ops):
                 or out_offset + m > out.shape[2]:
             raise KernelError(f"linear_heads: a {tuple(a.shape)} from {a_offset}, w {tuple(w.shape)}, out {tuple(out.shape)} at {out_offset}")
         es = a.element_size()
+        if self.use_tensor_cores and self.grouped_tensor_cores:
+            args = (c_void_p(a.data_ptr() + a_offset * es), c_longlong(heads * wa), c_longlong(wa), _p(w),
+                    c_void_p(out.data_ptr() + out_offset * es), c_longlong(heads * out.shape[2]), c_longlong(out.shape[2]))
+            if self.mix_tc.fz_grouped_tc_check(*args, c_int(m), c_int(k)) == 0:
+                self._check(self.mix_tc.fz_linear_heads_tc(*args, c_int(_CODE[self.dtype]), c_int(n), c_int(heads), c_int(m),
+                                                           c_int(k), self._stream()), "linear_heads (tensor cores)",
+                            (n * heads * (k + m) + heads * m * k) * es)
+                return
         self._check(self.mix.fz_linear_heads(
             c_void_p(a.data_ptr() + a_offset * es), c_longlong(heads * wa), c_longlong(wa), _p(w),
             c_void_p(out.data_ptr() + out_offset * es), c_longlong(heads * out.shape[2]), c_longlong(out.shape[2]),
@@ -709,23 +718,38 @@ class CudaOps(Ops):
         self._want(token_ids, "token ids", (torch.int32,), 1)
         self._want(table, "expert table", (torch.int32,), 2)
         n, top = token_ids.shape[0], table.shape[1]
+        # row tiles of 64 pairs; of 16 where an expert gets few rows (decoded tokens) and the tensor-core kernels run
         tile = int(self.mix.fz_grouped_tile_rows())
+        if self.use_tensor_cores and self.grouped_tensor_cores and n * top <= 16 * num_experts:
+            tile = 16
         max_tiles = -(-n * top // tile) + min(num_experts, n * top)
         idx = self._scratch("expert route", 2 * n * top + 3 * max_tiles, torch.int32)
         a_idx, c_idx, tiles = idx[:n * top], idx[n * top: 2 * n * top], idx[2 * n * top: 2 * n * top + 3 * max_tiles]
         self._check(self.mix.fz_route_by_table(_p(token_ids), _p(meta.seq_row), _p(table), c_int(n), c_int(table.shape[0]),
                                                c_int(top), c_int(num_experts), _p(a_idx), _p(c_idx), _p(tiles),
-                                               c_int(max_tiles), _p(self.err), self._stream()), "route_by_table")
-        return (a_idx, c_idx, tiles, max_tiles, n, top, meta.seq_row)
+                                               c_int(max_tiles), c_int(tile), _p(self.err), self._stream()), "route_by_table")
+        return (a_idx, c_idx, tiles, max_tiles, n, top, meta.seq_row, tile)
+
+    def _grouped_tc(self, a, lda, w, c, ldc, n_out, k) -> bool:
+        return bool(self.use_tensor_cores and self.grouped_tensor_cores and a.dtype == torch.bfloat16 and
+                    self.mix_tc.fz_grouped_tc_check(_p(a), c_longlong(lda), c_longlong(0), _p(w), _p(c), c_longlong(ldc),
+                                                    c_longlong(0), c_int(n_out), c_int(k)) == 0)
 
     def grouped_linear_glu(self, h, w, route, y, alpha, limit) -> None:
-        a_idx, c_idx, tiles, max_tiles, n, top, seq_row = route
+        a_idx, c_idx, tiles, max_tiles, n, top, seq_row, tile = route
         self._want(h, "expert input", (self.dtype,), 2)
         self._want(w, "expert gate/up weights", (self.dtype,), 3)
         self._want(y, "expert activation", (self.dtype,), 2)
         k, inter = h.shape[1], w.shape[1] // 2
         if h.shape[0] != n or w.shape[2] != k or w.shape[1] != 2 * inter or tuple(y.shape) != (n * top, inter):
             raise KernelError(f"grouped_linear_glu: h {tuple(h.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+        nbytes = (min(w.shape[0], n * top) * 2 * inter * k + n * k + n * top * inter) * h.element_size()
+        if self._grouped_tc(h, k, w, y, inter, inter, k):
+            self._check(self.mix_tc.fz_grouped_linear_tc(_p(h), _p(w), _p(y), _p(tiles), c_int(max_tiles), c_int(tile), _p(a_idx),
+                                                         c_void_p(0), c_int(_CODE[y.dtype]), c_int(inter), c_int(k), c_int(1),
+                                                         c_float(alpha), c_float(limit), c_void_p(0), c_int(0), c_int(0),
+                                                         self._stream()), "grouped_linear_glu (tensor cores)", nbytes)
+            return
         self._check(self.mix.fz_grouped_linear(_p(h), _p(w), _p(y), _p(tiles), c_int(max_tiles), _p(a_idx), c_void_p(0),
                                                c_int(_CODE[self.dtype]), c_int(_CODE[self.dtype]), c_int(inter), c_int(k),
                                                c_int(1), c_float(alpha), c_float(limit), c_void_p(0), c_int(0), c_int(0),
@@ -733,13 +757,20 @@ class CudaOps(Ops):
                     "grouped_linear_glu", (min(w.shape[0], n * top) * 2 * inter * k + n * k + n * top * inter) * h.element_size())
 
     def grouped_linear_scatter(self, y, w, route, out) -> None:
-        a_idx, c_idx, tiles, max_tiles, n, top, seq_row = route
+        a_idx, c_idx, tiles, max_tiles, n, top, seq_row, tile = route
         self._want(y, "expert activation", (self.dtype,), 2)
         self._want(w, "expert down weights", (self.dtype,), 3)
         self._want(out, "expert outputs", (torch.float32,), 2)
         inter, d = y.shape[1], w.shape[1]
         if y.shape[0] != n * top or w.shape[2] != inter or tuple(out.shape) != (n * top, d):
             raise KernelError(f"grouped_linear_scatter: y {tuple(y.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        nbytes = min(w.shape[0], n * top) * d * inter * y.element_size() + n * top * (inter * y.element_size() + d * 4)
+        if self._grouped_tc(y, inter, w, out, d, d, inter):
+            self._check(self.mix_tc.fz_grouped_linear_tc(_p(y), _p(w), _p(out), _p(tiles), c_int(max_tiles), c_int(tile),
+                                                         c_void_p(0), _p(c_idx), c_int(_CODE[out.dtype]), c_int(d), c_int(inter),
+                                                         c_int(0), c_float(0.0), c_float(0.0), _p(seq_row), c_int(n), c_int(top),
+                                                         self._stream()), "grouped_linear_scatter (tensor cores)", nbytes)
+            return
         self._check(self.mix.fz_grouped_linear(_p(y), _p(w), _p(out), _p(tiles), c_int(max_tiles), c_void_p(0), _p(c_idx),
                                                c_int(_CODE[self.dtype]), c_int(_CODE[torch.float32]), c_int(d), c_int(inter),
                                                c_int(0), c_float(0.0), c_float(0.0), _p(seq_row), c_int(n), c_int(top),

@@ -1,7 +1,7 @@
 """Parallel block with gated sublayers: `x += g1 * mixer(h1') + g2 * ffn(h2)`, both sublayers reading the same x.
 
 `h1 = norm1(x)`, `h2 = norm2(x)`; the mixer reads `h1' = h1 + conv(h1)` when the block has a short convolution
-(`taps` > 1; see `short_conv.ShortConv`), else h1; with `gated` each sublayer's result is multiplied element by element by
+(`taps` >= 1; see `short_conv.ShortConv`; with one tap it is a per-channel scale and keeps no state), else h1; with `gated` each sublayer's result is multiplied element by element by
 `sigmoid(W_g h + b_g)` of its own norm's output (before the convolution). A layer without a feed-forward has only the
 first term (and neither norm2 nor the second gate). The pending term of the previous layer is added by norm1, in the
 same pass over the row; gates, their sigmoid and the sum of the two terms are 32-bit.
@@ -19,7 +19,7 @@ _NAMES = {"norm1": "norm1", "norm2": "norm2", "mixer": "mixer", "ffn": "ffn", "c
 
 @register_block("parallel_gated")
 class ParallelGatedBlock(Block):
-    def __init__(self, mixer: Mixer, ffn: FeedForward | None, make_norm, hidden_size: int, taps: int = 1,
+    def __init__(self, mixer: Mixer, ffn: FeedForward | None, make_norm, hidden_size: int, taps: int = 0,
                  gated: bool = True, norms: tuple = (None, None), names: dict | None = None):
         self.mixer, self.ffn, self.D, self.gated = mixer, ffn, hidden_size, bool(gated)
         self.names = {**_NAMES, **(names or {})}
@@ -27,7 +27,7 @@ class ParallelGatedBlock(Block):
         self.norm2 = None
         if ffn is not None:
             self.norm2 = make_norm(norms[1]) if norms[1] is not None else make_norm()
-        self.conv = ShortConv(hidden_size, taps, name="") if taps > 1 else None
+        self.conv = ShortConv(hidden_size, taps, name="") if taps >= 1 else None      # taps 0: no convolution
         self.wg1 = self.bg1 = self.wg2 = self.bg2 = None
 
     def children(self):
@@ -44,11 +44,15 @@ class ParallelGatedBlock(Block):
 
     def tensors(self) -> dict[str, ParamSpec]:
         out = {(f"{prefix}.{k}" if k else prefix): v for prefix, part in self.children() for k, v in part.tensors().items()}
+        n, D = self.names, self.D
         if self.gated:
-            n, D = self.names, self.D
             for g in ("gate1", "gate2") if self.ffn is not None else ("gate1",):
                 out[n[g]] = ParamSpec((D, D))
                 out[f"{n[g]}.{n['bias']}"] = ParamSpec((D,), role="vector", init="zeros")
+        if self.ffn is None:      # what belongs to the absent feed-forward is passed over if a checkpoint carries it
+            out[n["norm2"]] = ParamSpec((D,), role="vector", ignore=True)
+            out[n["gate2"]] = ParamSpec((D, D), ignore=True)
+            out[f"{n['gate2']}.{n['bias']}"] = ParamSpec((D,), role="vector", ignore=True)
         return out
 
     def bind(self, tensors, ops) -> None:

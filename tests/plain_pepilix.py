@@ -96,13 +96,13 @@ def forward(cfg: dict, weights: dict, tokens, rounded: bool = False, layers_out:
     """Logits (T, vocab) of one whole sequence. rounded: matrices, matrix inputs and cache entries pass through bfloat16."""
     rnd = (lambda t: t.to(torch.bfloat16).to(F)) if rounded else (lambda t: t)
     W = {k: (v.long() if not v.dtype.is_floating_point else (rnd(v.to(F)) if v.dim() >= 2 else v.to(F))) for k, v in weights.items()}
-    eps, groups, taps = cfg["norm"]["eps"], cfg["norm"]["groups"], cfg["canon"]["taps"]
+    eps, groups, taps = cfg["norm"]["eps"], cfg["norm"]["groups"], (cfg.get("canon") or {}).get("taps", 0)
     x = W["embed"][torch.tensor(tokens)] * cfg["embedding"]["scale"]
     cached: dict[int, tuple] = {}
     for i, L in enumerate(cfg["layers"]):
         p, m = f"l{i}.", L["mixer"]
         h1 = rnd(grouped_rms_norm(x, W[p + "norm1"], groups, eps))
-        hm = rnd(h1 + causal_conv(h1, W[p + "canon1"])) if taps > 1 else h1
+        hm = rnd(h1 + causal_conv(h1, W[p + "canon1"])) if taps >= 1 else h1
         base, dims = m["rot"]["base"], m["rot"]["dims"]
         if m.get("kv_from") is None:
             cached[i] = latent_entries(hm, W[p + "mix.dkv"], W[p + "mix.dkv.norm"], m["kv_rank"], eps, base, dims, rnd)

@@ -111,3 +111,43 @@ def test_greedy_generation_through_the_entry_point_and_scheduler(dirs):
             row = lg[len(prompt) - 1 + i]
             assert row.max() - row[t] <= 1e-4 * np.abs(row).max()
     assert eng.cache.states.num_free == 2 and eng.cache.num_free_pages == 14
+
+
+@pytest.mark.parametrize("taps", [0, 1])
+def test_one_tap_and_no_convolution(tmp_path, taps):
+    """One tap is a per-channel scale of the mixer's input without state; a configuration without the key has no
+    convolution and no such tensor."""
+    from fusezap_core_b200.weights import write_random_model
+    from safetensors.torch import load_file
+    cfg = copy.deepcopy(PEP_SMALL)
+    if taps:
+        cfg["canon"] = {"taps": taps}
+    else:
+        del cfg["canon"]
+    d = write_random_model(cfg, str(tmp_path / "m"), 31, "float32", norm_noise=True, std_scale=4.0)
+    w = load_file(os.path.join(d, "model.safetensors"))
+    assert ("l0.canon1" in w) == bool(taps)
+    model, cache, runner = engine_parts(d)
+    assert model.state_needs() == {}
+    toks = tokens_for(cfg, (33,), seed=1)[0]
+    got = run_cut(runner, cache, "r", toks, [4, 1, 9])
+    assert rel_rms(got, plain_pepilix.forward(cfg, w, toks).numpy()) < LIMIT["float32"]
+
+
+def test_tensors_of_an_absent_feed_forward_are_passed_over(dirs, tmp_path):
+    """A checkpoint that carries a second norm and gate for a layer without feed-forward loads, and they change nothing."""
+    from fusezap_core_b200.weights.safetensors_io import write_file
+    d, cfg, w = dirs["small"]
+    more = dict(w)
+    more["l1.norm2"], more["l1.rg2"], more["l1.rg2.b"] = torch.ones(96), torch.ones(96, 96), torch.ones(96)
+    d2 = str(tmp_path / "m")
+    os.makedirs(d2)
+    with open(os.path.join(d2, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    write_file(os.path.join(d2, "model.safetensors"), more.items())
+    toks = tokens_for(cfg, (20,), seed=3)[0]
+    out = []
+    for folder in (d, d2):
+        model, cache, runner = engine_parts(folder)
+        out.append(run_cut(runner, cache, "r", toks, [20]))
+    assert np.array_equal(out[0], out[1])

@@ -152,25 +152,34 @@ def test_latent_cache_write_norms_rotates_and_lands_on_the_right_page(dtype, L, 
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_rotate_heads_and_products_per_head(dtype):
+@pytest.mark.parametrize("N,H,dn,dr,r,dims", [(70, 5, 12, 10, 24, 6), (300, 16, 64, 32, 128, 32), (5, 6, 32, 32, 128, 32),
+                                              (70, 3, 16, 8, 40, 8)])
+def test_rotate_heads_and_products_per_head(dtype, N, H, dn, dr, r, dims):
     from fusezap_core_b200.parts.rope import RotaryEncoding
     ops, g, dt = cuda_ops(dtype), torch.Generator().manual_seed(3), DT[dtype]
-    N, H, dn, dr, r, dims = 70, 5, 12, 10, 24, 6
     pos = RotaryEncoding(dims, 77.0, precise=True)
-    pos.prepare(256, torch.device(DEV))
-    meta = Meta([(69, 130, -1)], torch.zeros(1, 1, dtype=torch.int32), pad=1)
+    pos.prepare(512, torch.device(DEV))
+    meta = Meta([(N - 1, 130, -1)], torch.zeros(1, 1, dtype=torch.int32), pad=1)
     q = torch.randn(N, H, dn + dr, generator=g).to(dt)
     wt = torch.randn(H, r, dn, generator=g).to(dt)
     qa = torch.zeros(N, H, r + dr, dtype=dt, device=DEV)
     ops.rotate_heads(q.to(DEV), dn, pos.cos, pos.sin, dims, meta, qa, r)
     ops.linear_heads(q.to(DEV), 0, dn, wt.to(DEV), qa, 0)
-    ref_r = plain_pepilix.rotate(q[:69, :, dn:].to(F), torch.arange(130, 199), 77.0, dims)
+    ref_r = plain_pepilix.rotate(q[:N - 1, :, dn:].to(F), torch.arange(130, 129 + N), 77.0, dims)
     ref_n = torch.einsum("nhk,hmk->nhm", q[:, :, :dn].to(F), wt.to(F))
     tol = 1e-5 if dtype == "float32" else 2.0 ** -7
     got = qa.cpu().to(F)
-    assert ((got[:69, :, r:] - ref_r).abs() <= tol * (1 + ref_r.abs())).all()
-    assert float(got[69, :, r:].abs().max()) == 0.0
-    assert ((got[..., :r] - ref_n).abs() <= tol * (1 + ref_n.abs())).all()
+    assert ((got[:N - 1, :, r:] - ref_r).abs() <= tol * (1 + ref_r.abs())).all()
+    assert float(got[N - 1, :, r:].abs().max()) == 0.0
+    assert ((got[..., :r] - ref_n).abs() <= tol * (1 + ref_n.abs()) * max(1.0, dn ** 0.5 / 4)).all()
+    if dtype == "bfloat16":       # the plain kernel where the tensor-core one had taken the sizes
+        ops.grouped_tensor_cores = False
+        try:
+            qa2 = torch.zeros_like(qa)
+            ops.linear_heads(q.to(DEV), 0, dn, wt.to(DEV), qa2, 0)
+        finally:
+            ops.grouped_tensor_cores = True
+        assert ((qa2[..., :r].cpu().to(F) - ref_n).abs() <= tol * (1 + ref_n.abs()) * max(1.0, dn ** 0.5 / 4)).all()
 
 
 def _attention_reference(q, entries, Wv, scale, lo, p):
@@ -271,26 +280,35 @@ def test_window_edges(dtype, window):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("E,top,K,I,D", [(5, 1, 96, 24, 96), (4, 3, 64, 40, 72), (7, 7, 32, 8, 32), (12, 2, 320, 96, 320)])
-def test_table_routed_experts(dtype, E, top, K, I, D):
+@pytest.mark.parametrize("tensor_cores", [True, False])
+@pytest.mark.parametrize("E,top,K,I,D,N", [(5, 1, 96, 24, 96, 150), (4, 3, 64, 40, 72, 150), (7, 7, 32, 8, 32, 150),
+                                           (12, 2, 320, 96, 320, 150), (12, 2, 320, 96, 320, 7), (32, 4, 256, 128, 264, 40),
+                                           (3, 2, 20, 6, 10, 33)])
+def test_table_routed_experts(dtype, E, top, K, I, D, N, tensor_cores):
     """Rows sorted by expert on the device, each expert over its own rows, summed per row: against the plain loop. The
     inputs are scaled so that both clamps and the unclamped range occur."""
     ops, g, dt = cuda_ops(dtype), torch.Generator().manual_seed(E * top), DT[dtype]
-    N, V, limit = 150, 31, 0.8
+    if dtype == "float32" and not tensor_cores:
+        pytest.skip("the float32 path has the plain kernels only")
+    ops.grouped_tensor_cores = tensor_cores
+    V, limit = 31, 0.8
     h = torch.randn(N, K, generator=g).to(dt)
     wgu = (torch.randn(E, 2 * I, K, generator=g) * 0.12).to(dt)
     wd = (torch.randn(E, D, I, generator=g) * 0.2).to(dt)
     table = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(V)]).to(torch.int32)
     tok = torch.randint(0, V, (N,), generator=g).to(torch.int32)
-    meta = Meta([(100, 0, -1), (49, 5, -1)], torch.zeros(2, 1, dtype=torch.int32), pad=1)
+    k2 = (N - 1) // 3
+    meta = Meta([(N - 1 - k2, 0, -1), (k2, 5, -1)], torch.zeros(2, 1, dtype=torch.int32), pad=1)
     route = ops.route_by_table(tok.to(DEV), meta, table.to(DEV), E)
     y = torch.empty(N * top, I, dtype=dt, device=DEV)
     ops.grouped_linear_glu(h.to(DEV), wgu.to(DEV), route, y, 1.702, limit)
     terms = torch.full((N * top, D), float("nan"), device=DEV)
     ops.grouped_linear_scatter(y, wd.to(DEV), route, terms)
+    ops.grouped_tensor_cores = True
     ops.check_errors()
     rnd = (lambda t: t) if dtype == "float32" else (lambda t: t.to(torch.bfloat16).to(F))
     tol = 2e-5 if dtype == "float32" else 2.0 ** -6
+    tol *= max(1.0, (max(K, I) / 64) ** 0.5)
     for n in range(N - 1):
         for k in range(top):
             e = int(table[tok[n], k])
