@@ -31,7 +31,8 @@ __global__ void __launch_bounds__(THREADS)
 attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool,
                       const int* __restrict__ seg, int n_seg, const int* __restrict__ table, int mb,
                       long long page_stride, int page_size, int num_pages, __nv_bfloat16* __restrict__ out, int H, int W,
-                      int Wv, float scale_log2, int window, int* err) {
+                      int Wv, float scale_log2, int window, float* __restrict__ part_o, float* __restrict__ part_ml,
+                      int split_keys, int* err) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   constexpr int NBS = BN / 16;                 // 8-key blocks of S per warp (half the tile's keys)
@@ -54,8 +55,20 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
   const int valid = min(BM, n_rows * H - pair0);
   const int first_pos = pos0 + pair0 / H, last_pos = pos0 + (pair0 + valid - 1) / H;
   const int lo_tile = window > 0 ? max(0, first_pos - window + 1) : 0;
-  const int k_begin = lo_tile & ~(BN - 1);
-  const int ntiles = (last_pos - k_begin) / BN + 1;
+  // split_keys > 0: the keys are cut at multiples of split_keys and block (x, y) takes the y-th range; its result stays
+  // unnormalised in float32 scratch with the row's (max, sum), for the merge kernel
+  const int key_lo = split_keys > 0 ? max(lo_tile, (int)blockIdx.y * split_keys) : lo_tile;
+  const int key_hi = split_keys > 0 ? min(last_pos, ((int)blockIdx.y + 1) * split_keys - 1) : last_pos;
+  const size_t part = (size_t)blockIdx.x * gridDim.y + blockIdx.y;
+  if (key_lo > key_hi) {      // nothing of this range is visible to the tile (split mode only)
+    for (int r = threadIdx.x; r < BM; r += THREADS) {
+      part_ml[(part * BM + r) * 2] = -INFINITY;
+      part_ml[(part * BM + r) * 2 + 1] = 0.f;
+    }
+    return;
+  }
+  const int k_begin = key_lo & ~(BN - 1);
+  const int ntiles = (key_hi - k_begin) / BN + 1;
   const int* trow = table + (size_t)s_idx * mb;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rg = warp & 3, half = warp >> 2;
@@ -74,7 +87,7 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
     for (int e = tid; e < BN * chunks; e += THREADS) {
       const int r = e / chunks, c = e - r * chunks;
       const int key = key0 + r;
-      bool ok = key >= lo_tile && key <= last_pos;
+      bool ok = key >= key_lo && key <= key_hi;
       long long off = 0;
       if (ok) {
         const int pi = key / page_size;
@@ -124,7 +137,7 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
       for (int e = 0; e < 4; ++e) {
         const int key = key0 + kh0 + 8 * j + 2 * (lane & 3) + (e & 1);
         const int qpos = qp[e >> 1];
-        const bool ok = key <= qpos && (window <= 0 || key >= qpos - window + 1);
+        const bool ok = key <= qpos && key >= key_lo && key <= key_hi && (window <= 0 || key >= qpos - window + 1);
         const float v = ok ? s[j][e] * scale_log2 : -INFINITY;
         s[j][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -192,6 +205,25 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
     red[half * BM + r_lo + 8] = l_run[1];
   }
   __syncthreads();
+  if (split_keys > 0) {
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int r = r_lo + 8 * hh;
+      if (r >= valid) continue;
+      float* po = part_o + (part * BM + r) * Wv;
+#pragma unroll
+      for (int i = 0; i < 2 * NV16; ++i) {
+        const int col = (half * NV16 * 2 + i) * 8 + 2 * (lane & 3);
+        if (col < Wv) po[col] = o[i][2 * hh];
+        if (col + 1 < Wv) po[col + 1] = o[i][2 * hh + 1];
+      }
+      if (half == 0 && (lane & 3) == 0) {
+        part_ml[(part * BM + r) * 2] = m_run[hh];
+        part_ml[(part * BM + r) * 2 + 1] = red[r] + red[BM + r];
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int hh = 0; hh < 2; ++hh) {
     const int r = r_lo + 8 * hh;
@@ -204,6 +236,51 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
       if (col + 1 < Wv) *(uint32_t*)(orow + col) = pack_bf16(o[i][2 * hh] * inv, o[i][2 * hh + 1] * inv);
       else if (col < Wv) orow[col] = __float2bfloat16_rn(o[i][2 * hh] * inv);
     }
+  }
+}
+
+// Adds up a tile's key ranges: out = sum_y o_y 2^(m_y - m) / sum_y l_y 2^(m_y - m), m = max_y m_y.
+// One block per (tile, pair): a warp turns the ranges' (max, sum) into weights once, then every thread adds up its
+// columns with independent loads. n_split <= 32.
+__global__ void __launch_bounds__(128)
+attn_latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ seg,
+                         int n_seg, int n_split, __nv_bfloat16* __restrict__ out, int H, int Wv) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  __shared__ float w_s[32];
+  __shared__ float inv_s;
+  int s_idx = -1, pair0 = 0, b = blockIdx.x;
+  for (int s = 0; s < n_seg; ++s) {
+    const int t = (seg[4 * s + 1] * H + BM - 1) / BM;
+    if (b < t) { s_idx = s; pair0 = b * BM; break; }
+    b -= t;
+  }
+  if (s_idx < 0) return;
+  const int row0 = seg[4 * s_idx], valid = min(BM, seg[4 * s_idx + 1] * H - pair0);
+  const int r = blockIdx.y;
+  if (r >= valid) return;
+  const size_t base = (size_t)blockIdx.x * n_split;
+  if (threadIdx.x < 32) {
+    const int y = threadIdx.x;
+    const float my = y < n_split ? part_ml[((base + y) * BM + r) * 2] : -INFINITY;
+    const float ly = y < n_split ? part_ml[((base + y) * BM + r) * 2 + 1] : 0.f;
+    const float m = warp_max(my);
+    const float w = ly > 0.f ? exp2f(my - m) : 0.f;      // an empty range has sum 0 (its partial output was never written)
+    float l = ly * w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {                    // a prefix sum over the ranges: one fixed order of additions
+      const float up = __shfl_up_sync(0xffffffffu, l, o);
+      if (y >= o) l += up;
+    }
+    w_s[y] = w;
+    if (y == 31) inv_s = 1.0f / l;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < Wv; c += blockDim.x) {
+    float acc = 0.f;
+    for (int y = 0; y < n_split; ++y)
+      if (w_s[y] > 0.f) acc = fmaf(part_o[((base + y) * BM + r) * Wv + c], w_s[y], acc);
+    out[((size_t)row0 * H + pair0 + r) * Wv + c] = __float2bfloat16_rn(acc * inv_s);
   }
 }
 
@@ -222,8 +299,8 @@ size_t smem_bytes(int W, int bn) {
 
 template <int NV16, int BN>
 int launch(const void* q, const void* pool, const int* seg, int n_seg, const int* table, int mb, long long page_stride,
-           int page_size, int num_pages, void* out, int blocks, int H, int W, int Wv, float scale, int window, int* err,
-           cudaStream_t stream) {
+           int page_size, int num_pages, void* out, int blocks, int H, int W, int Wv, float scale, int window,
+           float* part_o, float* part_ml, int n_split, int split_keys, int* err, cudaStream_t stream) {
   const size_t smem = smem_bytes(W, BN);
   auto kern = attn_latent_tc_kernel<NV16, BN>;
   static size_t allowed = 48 * 1024;
@@ -232,9 +309,15 @@ int launch(const void* q, const void* pool, const int* seg, int n_seg, const int
     if (e != cudaSuccess) return (int)e;
     allowed = smem;
   }
-  fz_launch(kern, dim3(blocks), dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, seg, n_seg,
-            table, mb, page_stride, page_size, num_pages, (__nv_bfloat16*)out, H, W, Wv, scale * 1.4426950408889634f, window, err);
+  fz_launch(kern, dim3(blocks, n_split), dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, seg,
+            n_seg, table, mb, page_stride, page_size, num_pages, (__nv_bfloat16*)out, H, W, Wv, scale * 1.4426950408889634f,
+            window, part_o, part_ml, split_keys, err);
   FZ_LAUNCH_CHECK();
+  if (split_keys > 0) {
+    fz_launch(attn_latent_merge_kernel, dim3(blocks, BM), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, seg,
+              n_seg, n_split, (__nv_bfloat16*)out, H, Wv);
+    FZ_LAUNCH_CHECK();
+  }
   return FZ_OK;
 }
 
@@ -255,19 +338,40 @@ FZ_API int fz_attn_latent_tc_check(int H, int W, int Wv) {
   return FZ_OK;
 }
 
-// blocks: at least the number of 64-pair tiles of the step, sum over portions of ceil(rows * H / 64).
+// How a step of `blocks` tiles whose longest context is max_context is cut along the keys: the number of ranges (1: not
+// cut) for a GPU of `sms` multiprocessors. Few tiles with many keys behind them (decoded tokens) would leave most of the
+// GPU idle; ranges of at least 128 keys, at most 32 of them, enough for about two blocks per multiprocessor.
+FZ_API int fz_attn_latent_tc_splits(int blocks, int max_context, int sms) {
+  if (blocks <= 0 || blocks >= sms || max_context < 256) return 1;
+  int n = (2 * sms + blocks - 1) / blocks;
+  if (n > 32) n = 32;
+  if (n > max_context / 128) n = max_context / 128;
+  return n < 2 ? 1 : n;
+}
+
+// float32 scratch the cut needs: (outputs, then (max, sum) pairs), in floats.
+FZ_API long long fz_attn_latent_tc_scratch(int blocks, int n_split, int Wv) {
+  return n_split <= 1 ? 0 : (long long)blocks * n_split * BM * (Wv + 2);
+}
+
+// blocks: at least the number of 64-pair tiles of the step, sum over portions of ceil(rows * H / 64). n_split > 1: the
+// keys are cut into n_split ranges of equal length (a multiple of 64) that cover max_context; scratch as above.
 FZ_API int fz_attn_latent_tc(const void* q, const void* pool, const int* seq_row, const int* seg, int n_seg,
                              const int* table, int mb, long long page_stride, int page_size, int num_pages, void* out,
-                             int N, int blocks, int H, int W, int Wv, float scale, int window, int* err,
-                             cudaStream_t stream) {
+                             int N, int blocks, int H, int W, int Wv, float scale, int window, int n_split,
+                             int max_context, float* scratch, int* err, cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
   if (fz_attn_latent_tc_check(H, W, Wv) != FZ_OK || page_size <= 0) return FZ_BAD_SHAPE;
+  if (n_split < 1 || n_split > 65535 || (n_split > 1 && scratch == nullptr)) return FZ_BAD_SHAPE;
+  const int split_keys = n_split > 1 ? ((max_context + n_split - 1) / n_split + 63) / 64 * 64 : 0;
+  float* part_o = scratch;
+  float* part_ml = scratch ? scratch + (long long)blocks * n_split * BM * Wv : nullptr;
   fz_launch(zero_padding_rows_kernel, dim3(N), dim3(128), 0, stream, seq_row, (__nv_bfloat16*)out, N, H * Wv);
   FZ_LAUNCH_CHECK();
   if (blocks <= 0 || n_seg <= 0) return FZ_OK;
   const bool wide = smem_bytes(W, 64) <= 200 * 1024;
-#define FZ_GO(NV) return wide ? launch<NV, 64>(q, pool, seg, n_seg, table, mb, page_stride, page_size, num_pages, out, blocks, H, W, Wv, scale, window, err, stream) \
-                              : launch<NV, 32>(q, pool, seg, n_seg, table, mb, page_stride, page_size, num_pages, out, blocks, H, W, Wv, scale, window, err, stream)
+#define FZ_GO(NV) return wide ? launch<NV, 64>(q, pool, seg, n_seg, table, mb, page_stride, page_size, num_pages, out, blocks, H, W, Wv, scale, window, part_o, part_ml, n_split, split_keys, err, stream) \
+                              : launch<NV, 32>(q, pool, seg, n_seg, table, mb, page_stride, page_size, num_pages, out, blocks, H, W, Wv, scale, window, part_o, part_ml, n_split, split_keys, err, stream)
   switch (nv16_for(Wv)) {
     case 1: FZ_GO(1);
     case 2: FZ_GO(2);

@@ -10,14 +10,17 @@ __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf
 
 // ------------------------------------------------------------------------------------------------ add + grouped RMSNorm
 // As add_rmsnorm (rows == nullptr: x += delta in place; else row selection), with the row split into G equal
-// consecutive parts, each scaled by its own 1 / sqrt(mean(part^2) + eps). Warp w sums the parts w, w + W, ...: a part's
-// sum is a fixed chain per lane followed by the warp's butterfly, whatever else is in the step.
+// consecutive parts, each scaled by its own 1 / sqrt(mean(part^2) + eps). The block's 256 threads form teams of TEAM
+// threads (a power of two, at least a warp); team t sums the parts t, t + teams, ...: a part's sum is a fixed chain per
+// thread, the warp's butterfly, and the team's warps added in rising order, whatever else is in the step.
 template <typename TW, typename TH>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_groups_kernel(float* __restrict__ x, const float* __restrict__ delta, const TW* __restrict__ w,
-                          TH* __restrict__ h, const int* __restrict__ rows, int n_src, int D, int G, float eps, int* err) {
+                          TH* __restrict__ h, const int* __restrict__ rows, int n_src, int D, int G, int team, float eps,
+                          int* err) {
   fz_grid_launch_dependents();
   fz_grid_wait();
+  __shared__ float warp_ss[8];
   const int r = blockIdx.x;
   int src = r;
   TH* hr = h + (size_t)r * D;
@@ -29,26 +32,38 @@ add_rmsnorm_groups_kernel(float* __restrict__ x, const float* __restrict__ delta
       return;
     }
   }
-  float* xr = x + (size_t)src * D;
-  const float* dr = delta ? delta + (size_t)src * D : nullptr;
+  float* __restrict__ xr = x + (size_t)src * D;
+  const float* __restrict__ dr = delta ? delta + (size_t)src * D : nullptr;
   const bool write_x = rows == nullptr && dr != nullptr;
   const int Dg = D / G;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, W = blockDim.x >> 5;
-  for (int g = warp; g < G; g += W) {
+  const int teams = blockDim.x / team, t = threadIdx.x / team, lt = threadIdx.x - t * team;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpt = team >> 5;     // warps per team
+  for (int g0 = 0; g0 < G; g0 += teams) {       // the same trip count for every thread: the barriers below are safe
+    const int g = g0 + t;
     float ss = 0.f;
-    for (int d = g * Dg + lane; d < (g + 1) * Dg; d += 32) {
-      float v = xr[d];
-      if (dr) v += dr[d];
-      if (write_x) xr[d] = v;
-      ss = fmaf(v, v, ss);
+    if (g < G) {
+#pragma unroll 4
+      for (int d = g * Dg + lt; d < (g + 1) * Dg; d += team) {
+        float v = xr[d];
+        if (dr) v += dr[d];
+        if (write_x) xr[d] = v;
+        ss = fmaf(v, v, ss);
+      }
     }
     ss = warp_sum(ss);
-    const float scale = 1.0f / sqrtf(ss * (1.0f / (float)Dg) + eps);
-    for (int d = g * Dg + lane; d < (g + 1) * Dg; d += 32) {
-      float v = xr[d];
-      if (dr && !write_x) v += dr[d];
-      hr[d] = Cvt<TH>::from_f(Cvt<TW>::to_f(w[d]) * (v * scale));
-    }
+    __syncthreads();
+    if (lane == 0) warp_ss[warp] = ss;
+    __syncthreads();
+    float total = 0.f;
+    for (int i = 0; i < wpt; ++i) total += warp_ss[t * wpt + i];
+    const float scale = 1.0f / sqrtf(total * (1.0f / (float)Dg) + eps);
+    if (g < G)
+#pragma unroll 4
+      for (int d = g * Dg + lt; d < (g + 1) * Dg; d += team) {
+        float v = xr[d];
+        if (dr && !write_x) v += dr[d];
+        hr[d] = Cvt<TH>::from_f(Cvt<TW>::to_f(w[d]) * (v * scale));
+      }
   }
 }
 
@@ -64,14 +79,16 @@ short_conv_kernel(const T* __restrict__ h, const T* __restrict__ w, const float*
   const int n = blockIdx.x;
   const int s = seq_row[n];
   T* orow = out + (size_t)n * C;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;      // a thread per channel: grid (rows, channel blocks)
+  if (c >= C) return;
   if (s < 0) {
-    for (int c = threadIdx.x; c < C; c += blockDim.x) orow[c] = Cvt<T>::from_f(0.f);
+    orow[c] = Cvt<T>::from_f(0.f);
     return;
   }
   const int row0 = seg[4 * s], slot = seg[4 * s + 3];
   const int i = n - row0;
   const float* st = state != nullptr && slot >= 0 ? state + (size_t)slot * (taps - 1) * C : nullptr;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  {
     float acc = 0.f;
     for (int j = 0; j < taps; ++j) {
       const int k = i - (taps - 1) + j;
@@ -242,9 +259,12 @@ FZ_API int fz_add_rmsnorm_groups(float* x, const float* delta, const void* w, in
                                  cudaStream_t stream) {
   if (n_out <= 0) return FZ_OK;
   if (G <= 0 || D % G) return FZ_BAD_SHAPE;
-  const int threads = G >= 8 ? 256 : 32 * G;
-#define FZ_GN(TW, TH) do { fz_launch(add_rmsnorm_groups_kernel<TW, TH>, dim3(n_out), dim3(threads), 0, stream, x, delta, \
-    (const TW*)w, (TH*)h, rows, n_src, D, G, eps, err); FZ_LAUNCH_CHECK(); return FZ_OK; } while (0)
+  // teams of 256, 128, 64 or 32 threads: the largest that still gives every part a team in one pass, but no more
+  // threads than a part has values
+  int team = 256;
+  while (team > 32 && (256 / team < G || team > D / G)) team >>= 1;
+#define FZ_GN(TW, TH) do { fz_launch(add_rmsnorm_groups_kernel<TW, TH>, dim3(n_out), dim3(256), 0, stream, x, delta, \
+    (const TW*)w, (TH*)h, rows, n_src, D, G, team, eps, err); FZ_LAUNCH_CHECK(); return FZ_OK; } while (0)
   if (w_dtype == FZ_F32 && h_dtype == FZ_F32) FZ_GN(float, float);
   if (w_dtype == FZ_F32 && h_dtype == FZ_BF16) FZ_GN(float, __nv_bfloat16);
   if (w_dtype == FZ_BF16 && h_dtype == FZ_BF16) FZ_GN(__nv_bfloat16, __nv_bfloat16);
@@ -258,12 +278,12 @@ FZ_API int fz_short_conv(const void* h, const void* w, float* state, const int* 
   if (N <= 0) return FZ_OK;
   if (taps < 1 || taps > MAX_TAPS) return FZ_BAD_SHAPE;
   if (dtype == FZ_F32) {
-    fz_launch(short_conv_kernel<float>, dim3(N), dim3(256), 0, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual);
+    fz_launch(short_conv_kernel<float>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual);
     FZ_LAUNCH_CHECK();
     if (taps > 1 && state != nullptr && n_seg > 0)
       fz_launch(short_conv_state_kernel<float>, dim3(n_seg, (C + 255) / 256), dim3(256), 0, stream, (const float*)h, state, seg, C, taps);
   } else if (dtype == FZ_BF16) {
-    fz_launch(short_conv_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual);
+    fz_launch(short_conv_kernel<__nv_bfloat16>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual);
     FZ_LAUNCH_CHECK();
     if (taps > 1 && state != nullptr && n_seg > 0)
       fz_launch(short_conv_state_kernel<__nv_bfloat16>, dim3(n_seg, (C + 255) / 256), dim3(256), 0, stream, (const __nv_bfloat16*)h, state, seg, C, taps);

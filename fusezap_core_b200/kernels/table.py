@@ -126,6 +126,7 @@ class CudaOps(Ops):
         self.fuse_argmax = True            # lm_head product and argmax in one pass where no logits are asked for
         self.fuse_rope = True              # q/k/v product, rotation and cache write in one kernel (few-token steps)
         self.grouped_tensor_cores = True   # products per head and per expert on tensor cores where the sizes allow it
+        self.latent_key_cuts = True        # latent attention: few tiles with many keys are cut along the keys
         self.latent_tensor_cores = True    # latent attention on tensor cores where the sizes allow it (bfloat16)
         self.cut_prefill_keys = True       # few query tiles with many keys behind them are cut along the keys
         self._profile = None               # a StepProfile while the engine profiles its steps
@@ -700,12 +701,22 @@ class CudaOps(Ops):
         if self.use_tensor_cores and self.latent_tensor_cores and \
                 self.mix_tc.fz_attn_latent_tc_check(c_int(heads), c_int(width), c_int(value_width)) == 0:
             blocks = n * heads // 64 + max(1, int(getattr(meta, "latent_extra", 0)) or n)
+            # few tiles with many keys behind them (decoded tokens): the keys are cut into ranges, merged by a second kernel
+            ctx = max(1, int(meta.max_context))
+            splits = int(self.mix_tc.fz_attn_latent_tc_splits(c_int(blocks), c_int(ctx), c_int(self._sms))) if self.latent_key_cuts else 1
+            scratch = None
+            if splits > 1:
+                self.mix_tc.fz_attn_latent_tc_scratch.restype = c_longlong
+                scratch = self._scratch("latent attention partials",
+                                        int(self.mix_tc.fz_attn_latent_tc_scratch(c_int(blocks), c_int(splits), c_int(value_width))),
+                                        torch.float32)
             self._check(self.mix_tc.fz_attn_latent_tc(
                 _p(q), _p(pool), _p(meta.seq_row), _p(meta.seg), c_int(meta.n_segments), _p(table), c_int(table.shape[1]),
                 c_longlong(page_stride), c_int(cache.page_size), c_int(pool.shape[0]), _p(out), c_int(n), c_int(blocks),
-                c_int(heads), c_int(width), c_int(value_width), c_float(scale), c_int(window), _p(self.err), self._stream()),
+                c_int(heads), c_int(width), c_int(value_width), c_float(scale), c_int(window), c_int(splits), c_int(ctx),
+                _p(scratch), _p(self.err), self._stream()),
                 "latent_attention (tensor cores)", nbytes)
-            self.launches += 1    # the kernel that zeroes rows of padding
+            self.launches += 2 if splits > 1 else 1    # the kernel that zeroes rows of padding, the merge kernel
             return
         self._check(self.mix.fz_attn_latent(
             _p(q), _p(pool), _p(meta.pos), _p(meta.seq_row), _p(table), c_int(table.shape[1]), c_longlong(page_stride),

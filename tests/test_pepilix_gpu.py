@@ -35,6 +35,7 @@ class Meta:
         self.pos = torch.tensor(pos, dtype=torch.int32, device=DEV)
         self.seg = torch.tensor(seg, dtype=torch.int32, device=DEV)
         self.n_segments, self.n_rows = len(portions), at + pad
+        self.max_context = max(p0 + n for n, p0, _ in portions)
         self._table = tables.to(DEV)
 
         class Sg:
@@ -217,14 +218,15 @@ def test_latent_attention_rows_of_any_portion(dtype, H, W, Wv, page):
         ref = _attention_reference(q[i], ent[s], Wv, 0.3, 0, p)
         assert ((out[i].cpu().to(F) - ref).abs() <= tol * (1 + ref.abs())).all(), f"row {i}"
     assert float(out[46].float().abs().max()) == 0.0
-    if dtype == "bfloat16":       # the general kernel, where the tensor-core one had taken the sizes: the same within rounding
-        ops.latent_tensor_cores = False
-        try:
-            out2 = torch.empty_like(out)
-            ops.latent_attention(q.to(DEV), LayerCache(keys=pool, group=0, page_size=page), meta, out2, Wv, 0.3, 0)
-        finally:
-            ops.latent_tensor_cores = True
-        assert (out2.float() - out.float()).abs().max() <= 2.0 ** -5
+    if dtype == "bfloat16":       # the tensor-core kernel without its cut along the keys, and the general kernel: the same
+        for knob in ("latent_key_cuts", "latent_tensor_cores"):      # within rounding
+            setattr(ops, knob, False)
+            try:
+                out2 = torch.empty_like(out)
+                ops.latent_attention(q.to(DEV), LayerCache(keys=pool, group=0, page_size=page), meta, out2, Wv, 0.3, 0)
+            finally:
+                setattr(ops, knob, True)
+            assert (out2.float() - out.float()).abs().max() <= 2.0 ** -5, knob
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
