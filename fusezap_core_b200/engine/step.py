@@ -271,7 +271,9 @@ class StepRunner:
         if meta.n_wanted:
             h = model.final_norm.forward(ctx, x, delta, rows=meta.sel, n_rows=meta.n_wanted)
             transform = model.logit_transform
-            fused = getattr(self.ops, "linear_argmax", None) if ids_out is not None and transform is None else None
+            # (a transform that keeps the order of a row's logits does not change which one is largest)
+            plain = transform is None or getattr(transform, "keeps_order", False)
+            fused = getattr(self.ops, "linear_argmax", None) if ids_out is not None and plain else None
             if fused is not None and fused(h, model.lm_head, None, ids_out):
                 return None
             self.ops.linear(h, model.lm_head, None, logits)

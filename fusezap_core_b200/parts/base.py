@@ -164,6 +164,7 @@ class Block(Part):
 
 class LogitTransform(Part):
     """Changes the logits of the wanted rows, (R, vocab) float32, in place (a soft cap, a scale, a bias...). With one in
-    the model the output product always writes its logits (no fused argmax)."""
+    the model the output product always writes its logits (no fused argmax), unless the transform sets `keeps_order`
+    (it never changes which logit of a row is the largest)."""
     def forward(self, ctx: "StepContext", logits: torch.Tensor) -> None:
         raise NotImplementedError
