@@ -41,7 +41,7 @@ def add_engine_options(s: argparse.ArgumentParser) -> None:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="fusezap_core_b200", description="B200-native engine for the dense Llama / Qwen2.5 decoder")
+    ap = argparse.ArgumentParser(prog="fusezap_core_b200", description="B200-native engine for the dense Llama / Qwen2.5 decoder and for Pepilix")
     sub = ap.add_subparsers(dest="cmd", required=True)
     g = sub.add_parser("generate", help="generate tokens for prompts given as token ids")
     g.add_argument("model", nargs="?", default=None, help="model folder (config.json + safetensors)")
@@ -141,7 +141,10 @@ def cmd_random_weights(a: argparse.Namespace) -> int:
         with open(a.config) as f:
             cfg = json.load(f)
     if a.num_layers:
-        cfg["num_hidden_layers"] = a.num_layers
+        if isinstance(cfg.get("layers"), list):      # a configuration that lists its layers: the first --num-layers of them
+            cfg["layers"] = cfg["layers"][:a.num_layers]
+        else:
+            cfg["num_hidden_layers"] = a.num_layers
     write_random_model(cfg, a.out, a.seed, a.dtype, a.norm_noise)
     print(f"fusezap_core_b200: wrote {a.out} (seed {a.seed}, {a.dtype})", file=sys.stderr)
     return 0

@@ -43,8 +43,10 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
   const uint32_t s_p = s_k + 2 * BN * stride * 2;               // [BM][pstride]
   float* red = (float*)(smem + (size_t)BM * stride * 2 + (size_t)2 * BN * stride * 2 + (size_t)BM * pstride * 2);   // [2][BM]
 
-  // which portion, and which 64 pairs of it
-  int s_idx = -1, pair0 = 0, b = blockIdx.x;
+  // which portion, and which 64 pairs of it. Blocks are handed out in rising blockIdx.x: the tile index falls with it,
+  // so a prompt's last tiles, which have the most keys behind them, start first and the short ones fill the tail.
+  const int tile = gridDim.x - 1 - blockIdx.x;
+  int s_idx = -1, pair0 = 0, b = tile;
   for (int s = 0; s < n_seg; ++s) {
     const int t = (seg[4 * s + 1] * H + BM - 1) / BM;
     if (b < t) { s_idx = s; pair0 = b * BM; break; }
@@ -59,7 +61,7 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
   // unnormalised in float32 scratch with the row's (max, sum), for the merge kernel
   const int key_lo = split_keys > 0 ? max(lo_tile, (int)blockIdx.y * split_keys) : lo_tile;
   const int key_hi = split_keys > 0 ? min(last_pos, ((int)blockIdx.y + 1) * split_keys - 1) : last_pos;
-  const size_t part = (size_t)blockIdx.x * gridDim.y + blockIdx.y;
+  const size_t part = (size_t)tile * gridDim.y + blockIdx.y;
   if (key_lo > key_hi) {      // nothing of this range is visible to the tile (split mode only)
     for (int r = threadIdx.x; r < BM; r += THREADS) {
       part_ml[(part * BM + r) * 2] = -INFINITY;
@@ -115,10 +117,12 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
     __syncthreads();
     const uint32_t sk = s_k + (t & 1) * BN * stride * 2;
     const int key0 = k_begin + t * BN, kh0 = half * (BN / 2);    // this warp's keys of the tile: kh0 .. kh0 + BN/2 - 1
-    float s[NBS][4];
+    // two sets of accumulators, for even and odd k-steps: consecutive MMAs do not wait on each other, and with the loop
+    // unrolled the loads of the next k-steps are issued under the MMAs of this one
+    float s[NBS][4], s2[NBS][4];
 #pragma unroll
-    for (int j = 0; j < NBS; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
-    for (int ks = 0; ks < ksteps; ++ks) {
+    for (int j = 0; j < NBS; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; s2[j][0] = s2[j][1] = s2[j][2] = s2[j][3] = 0.f; }
+    auto k_step = [&](int ks, float (*acc)[4]) {
       uint32_t qf[4];
       ldmatrix_x4(qf, at(s_q, rg * 16 + (lane & 15), ks * 2 + (lane >> 4), stride));
 #pragma unroll
@@ -126,10 +130,19 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
         uint32_t kf[4];
         const int mi = lane >> 3;
         ldmatrix_x4(kf, at(sk, kh0 + jb * 16 + (mi >> 1) * 8 + (lane & 7), ks * 2 + (mi & 1), stride));
-        mma_bf16(s[2 * jb], qf, kf[0], kf[1]);
-        mma_bf16(s[2 * jb + 1], qf, kf[2], kf[3]);
+        mma_bf16(acc[2 * jb], qf, kf[0], kf[1]);
+        mma_bf16(acc[2 * jb + 1], qf, kf[2], kf[3]);
       }
+    };
+    int ks = 0;
+#pragma unroll 2
+    for (; ks + 1 < ksteps; ks += 2) {
+      k_step(ks, s);
+      k_step(ks + 1, s2);
     }
+    if (ks < ksteps) k_step(ks, s);
+#pragma unroll
+    for (int j = 0; j < NBS; ++j) { s[j][0] += s2[j][0]; s[j][1] += s2[j][1]; s[j][2] += s2[j][2]; s[j][3] += s2[j][3]; }
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int j = 0; j < NBS; ++j)

@@ -38,16 +38,39 @@ add_rmsnorm_groups_kernel(float* __restrict__ x, const float* __restrict__ delta
   const int Dg = D / G;
   const int teams = blockDim.x / team, t = threadIdx.x / team, lt = threadIdx.x - t * team;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpt = team >> 5;     // warps per team
+  constexpr int KEEP = 8;                        // values a thread keeps in registers between the two passes
+  const bool keep = Dg <= KEEP * team;           // (else the second pass reads the row again)
   for (int g0 = 0; g0 < G; g0 += teams) {       // the same trip count for every thread: the barriers below are safe
     const int g = g0 + t;
+    const int end = (g + 1) * Dg;
     float ss = 0.f;
-    if (g < G) {
+    float v[KEEP];
+    if (g < G && keep) {
+#pragma unroll
+      for (int i = 0; i < KEEP; ++i) {
+        const int d = g * Dg + lt + i * team;
+        v[i] = d < end ? xr[d] : 0.f;
+      }
+      if (dr) {
+#pragma unroll
+        for (int i = 0; i < KEEP; ++i) {
+          const int d = g * Dg + lt + i * team;
+          if (d < end) v[i] += dr[d];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < KEEP; ++i) {
+        const int d = g * Dg + lt + i * team;
+        if (write_x && d < end) xr[d] = v[i];
+        ss = fmaf(v[i], v[i], ss);
+      }
+    } else if (g < G) {
 #pragma unroll 4
-      for (int d = g * Dg + lt; d < (g + 1) * Dg; d += team) {
-        float v = xr[d];
-        if (dr) v += dr[d];
-        if (write_x) xr[d] = v;
-        ss = fmaf(v, v, ss);
+      for (int d = g * Dg + lt; d < end; d += team) {
+        float u = xr[d];
+        if (dr) u += dr[d];
+        if (write_x) xr[d] = u;
+        ss = fmaf(u, u, ss);
       }
     }
     ss = warp_sum(ss);
@@ -57,13 +80,20 @@ add_rmsnorm_groups_kernel(float* __restrict__ x, const float* __restrict__ delta
     float total = 0.f;
     for (int i = 0; i < wpt; ++i) total += warp_ss[t * wpt + i];
     const float scale = 1.0f / sqrtf(total * (1.0f / (float)Dg) + eps);
-    if (g < G)
-#pragma unroll 4
-      for (int d = g * Dg + lt; d < (g + 1) * Dg; d += team) {
-        float v = xr[d];
-        if (dr && !write_x) v += dr[d];
-        hr[d] = Cvt<TH>::from_f(Cvt<TW>::to_f(w[d]) * (v * scale));
+    if (g < G && keep) {
+#pragma unroll
+      for (int i = 0; i < KEEP; ++i) {
+        const int d = g * Dg + lt + i * team;
+        if (d < end) hr[d] = Cvt<TH>::from_f(Cvt<TW>::to_f(w[d]) * (v[i] * scale));
       }
+    } else if (g < G) {
+#pragma unroll 4
+      for (int d = g * Dg + lt; d < end; d += team) {
+        float u = xr[d];
+        if (dr && !write_x) u += dr[d];
+        hr[d] = Cvt<TH>::from_f(Cvt<TW>::to_f(w[d]) * (u * scale));
+      }
+    }
   }
 }
 

@@ -151,3 +151,22 @@ def test_tensors_of_an_absent_feed_forward_are_passed_over(dirs, tmp_path):
         model, cache, runner = engine_parts(folder)
         out.append(run_cut(runner, cache, "r", toks, [20]))
     assert np.array_equal(out[0], out[1])
+
+
+def test_command_line_writes_a_preset_and_the_engine_loads_it(tmp_path):
+    from fusezap_core_b200.cli import main, presets
+    assert "tiny-pepilix" in presets()
+    out = str(tmp_path / "m")
+    assert main(["random-weights", "--preset", "tiny-pepilix", "--out", out, "--seed", "4", "--dtype", "float32", "--num-layers", "2"]) == 0
+    with open(os.path.join(out, "config.json")) as f:
+        cfg = json.load(f)
+    assert len(cfg["layers"]) == 2 and cfg["layers"][1]["mixer"]["kv_from"] == 0
+    from safetensors.torch import load_file
+    w = load_file(os.path.join(out, "model.safetensors"))
+    model, cache, runner = engine_parts(out)
+    toks = tokens_for(cfg, (19,), seed=6)[0]
+    got = run_cut(runner, cache, "r", toks, [6, 1, 12])
+    assert np.isfinite(got).all() and got.shape == (19, 512)
+    # weights of N(0, 0.02) make small logits: the difference is judged against the residual's size, not theirs
+    ref = plain_pepilix.forward(cfg, w, toks).numpy()
+    assert np.abs(got - ref).max() <= 1e-5 * max(1.0, np.abs(ref).max())

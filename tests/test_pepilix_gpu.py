@@ -394,3 +394,13 @@ def test_greedy_generation_through_the_entry_point_and_scheduler(dirs, dtype):
     model_ops = eng.model.ops
     model_ops.check_errors()
     assert eng.cache.states.num_free == 3 and eng.cache.num_free_pages == 20
+
+
+def test_command_line_generates_from_a_preset_with_random_weights(capsys):
+    import json
+    from fusezap_core_b200.cli import main
+    assert main(["generate", "--random", "tiny-pepilix", "--prompt-lens", "5,40,1", "--max-tokens", "6", "--ignore-eos",
+                 "--max-model-len", "128", "--num-blocks", "32", "--max-num-seqs", "2"]) == 0
+    lines = [json.loads(x) for x in capsys.readouterr().out.splitlines() if x.startswith("{")]
+    assert [o["num_prompt_tokens"] for o in lines] == [5, 40, 1]
+    assert all(len(o["token_ids"]) == 6 and o["finish_reason"] == "length" for o in lines)
