@@ -26,6 +26,33 @@ __device__ __forceinline__ uint32_t at(uint32_t base, int row, int chunk, int st
   return base + (uint32_t)(row * stride * 2 + chunk * 16);
 }
 
+// Which portion holds tile `tile` (tiles are numbered portion by portion, ceil(rows * H / 64) each), and the tile's first
+// pair within it. Every warp works it out for itself: 32 portions per round, a lane loads one portion's row count, a
+// prefix sum over the lanes, a ballot for the first portion whose tiles reach past `tile`. Returns -1 if there is none.
+__device__ __forceinline__ int locate_tile(const int* __restrict__ seg, int n_seg, int H, int tile, int& pair0) {
+  const int lane = threadIdx.x & 31;
+  int base = 0;
+  for (int s0 = 0; s0 < n_seg; s0 += 32) {
+    const int s = s0 + lane;
+    const int mine = s < n_seg ? (seg[4 * s + 1] * H + BM - 1) / BM : 0;
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    const unsigned hit = __ballot_sync(0xffffffffu, tile < base + incl);
+    if (hit) {
+      const int first = __ffs(hit) - 1;
+      const int before = base + __shfl_sync(0xffffffffu, incl - mine, first);
+      pair0 = (tile - before) * BM;
+      return s0 + first;
+    }
+    base += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  return -1;
+}
+
 template <int NV16, int BN>      // a warp's value columns: NV16 * 16; keys per tile: BN
 __global__ void __launch_bounds__(THREADS)
 attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool,
@@ -46,12 +73,8 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
   // which portion, and which 64 pairs of it. Blocks are handed out in rising blockIdx.x: the tile index falls with it,
   // so a prompt's last tiles, which have the most keys behind them, start first and the short ones fill the tail.
   const int tile = gridDim.x - 1 - blockIdx.x;
-  int s_idx = -1, pair0 = 0, b = tile;
-  for (int s = 0; s < n_seg; ++s) {
-    const int t = (seg[4 * s + 1] * H + BM - 1) / BM;
-    if (b < t) { s_idx = s; pair0 = b * BM; break; }
-    b -= t;
-  }
+  int pair0 = 0;
+  const int s_idx = locate_tile(seg, n_seg, H, tile, pair0);
   if (s_idx < 0) return;
   const int row0 = seg[4 * s_idx], n_rows = seg[4 * s_idx + 1], pos0 = seg[4 * s_idx + 2];
   const int valid = min(BM, n_rows * H - pair0);
@@ -83,23 +106,23 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
       cp_async16(at(s_q, r, c, stride), qbase + (size_t)r * W + c * 8, r < valid);
     }
   }
+  // A key row of the tile is copied by THREADS / BN threads, each looking the row's page up once (the lookup is a load
+  // from global memory that the copies depend on: one per thread and tile, not one per 16 bytes).
+  constexpr int TPR = THREADS / BN;
+  const int my_row = tid / TPR, my_sub = tid - my_row * TPR;
   auto issue = [&](int t) {
     const uint32_t st = s_k + (t & 1) * BN * stride * 2;
-    const int key0 = k_begin + t * BN;
-    for (int e = tid; e < BN * chunks; e += THREADS) {
-      const int r = e / chunks, c = e - r * chunks;
-      const int key = key0 + r;
-      bool ok = key >= key_lo && key <= key_hi;
-      long long off = 0;
-      if (ok) {
-        const int pi = key / page_size;
-        const int page = trow[pi];
-        ok = page >= 0 && page < num_pages;
-        if (!ok) atomicOr(err, FZ_ERR_NO_PAGE);
-        else off = (long long)page * page_stride + (long long)(key - pi * page_size) * W + c * 8;
-      }
-      cp_async16(at(st, r, c, stride), pool + off, ok);
+    const int key = k_begin + t * BN + my_row;
+    bool ok = key >= key_lo && key <= key_hi;
+    const __nv_bfloat16* src = pool;
+    if (ok) {
+      const int pi = key / page_size;
+      const int page = trow[pi];
+      ok = page >= 0 && page < num_pages;
+      if (!ok) atomicOr(err, FZ_ERR_NO_PAGE);
+      else src = pool + (long long)page * page_stride + (long long)(key - pi * page_size) * W;
     }
+    for (int c = my_sub; c < chunks; c += TPR) cp_async16(at(st, my_row, c, stride), ok ? src + c * 8 : pool, ok);
     cp_async_commit();
   };
   issue(0);
@@ -262,12 +285,8 @@ attn_latent_merge_kernel(const float* __restrict__ part_o, const float* __restri
   fz_grid_wait();
   __shared__ float w_s[32];
   __shared__ float inv_s;
-  int s_idx = -1, pair0 = 0, b = blockIdx.x;
-  for (int s = 0; s < n_seg; ++s) {
-    const int t = (seg[4 * s + 1] * H + BM - 1) / BM;
-    if (b < t) { s_idx = s; pair0 = b * BM; break; }
-    b -= t;
-  }
+  int pair0 = 0;
+  const int s_idx = locate_tile(seg, n_seg, H, blockIdx.x, pair0);
   if (s_idx < 0) return;
   const int row0 = seg[4 * s_idx], valid = min(BM, seg[4 * s_idx + 1] * H - pair0);
   const int r = blockIdx.y;

@@ -215,7 +215,7 @@ FZ_API int fz_route_by_table(const int* token_ids, const int* seq_row, const int
                              int* a_idx, int* c_idx, int* tiles, int max_tiles, int tile_rows, int* err,
                              cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
-  if (E <= 0 || E > 4096 || top <= 0 || tile_rows <= 0 || tile_rows > BM) return FZ_BAD_SHAPE;
+  if (E <= 0 || E > 4096 || top <= 0 || tile_rows <= 0 || tile_rows > 128) return FZ_BAD_SHAPE;
   fz_launch(route_by_table_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int), stream, token_ids, seq_row, table, N, V,
             top, E, a_idx, c_idx, tiles, max_tiles, tile_rows, err);
   FZ_LAUNCH_CHECK();
@@ -224,11 +224,11 @@ FZ_API int fz_route_by_table(const int* token_ids, const int* seq_row, const int
 
 // Experts mode. glu != 0: W (E, 2N, K), C (pairs, N) in sorted order, A rows through a_idx. glu == 0: W (E, N, K), A
 // (pairs, K) in sorted order, C rows through c_idx; pad_rows (may be null): see GroupedArgs.
-FZ_API int fz_grouped_linear(const void* A, const void* W, void* C, const int* tiles, int max_tiles, const int* a_idx,
+FZ_API int fz_grouped_linear(const void* A, const void* W, void* C, const int* tiles, int max_tiles, int tile_rows, const int* a_idx,
                              const int* c_idx, int in_dtype, int out_dtype, int N, int K, int glu, float alpha,
                              float limit, const int* pad_rows, int pad_n, int pad_top, cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0) return FZ_OK;
-  if (K <= 0) return FZ_BAD_SHAPE;
+  if (K <= 0 || tile_rows > BM) return FZ_BAD_SHAPE;      // a tile list built for larger row tiles than this kernel's
   if (max_tiles > 65535) return FZ_TOO_LARGE;
   GroupedArgs p = {A, K, 0, W, (long long)(glu ? 2 : 1) * N * K, C, N, 0, 0, N, K, tiles, a_idx, c_idx, alpha, limit, pad_rows, pad_n, pad_top};
   return dispatch(p, dim3((N + BN - 1) / BN, max_tiles, 1), in_dtype, out_dtype, glu != 0, stream);

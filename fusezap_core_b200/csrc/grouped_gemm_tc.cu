@@ -4,9 +4,11 @@
 // kernels of grouped_gemm.cu; a row's result does not depend on the tile it lands in (every output is the sum over k in
 // the fixed order of the 16-wide MMA steps).
 //
-// A block of four warps computes ROWS x 64 outputs, k in slices of 32 through a three-stage cp.async ring. ROWS = 64:
-// warp w owns rows 16 w .. 16 w + 15 and all 64 columns (many rows per group: prompts). ROWS = 16: every warp owns the
-// 16 rows and 16 of the columns (few rows per group: decoded tokens, where the weights are read once whatever the rows).
+// A block computes ROWS x 64 outputs, k in slices of 32 through a three-stage cp.async ring. ROWS = 64 (four warps) or
+// 128 (eight): warp w owns rows 16 w .. 16 w + 15 and all 64 columns (many rows per group: prompts; with 64 x 64 tiles
+// the products of a 2,048-token step draw their operands from L2 at about 5 TB/s and are bound by that, so groups with
+// hundreds of rows take 128). ROWS = 16: each of four warps owns the 16 rows and 16 of the columns (few rows per group:
+// decoded tokens, where the weights are read once whatever the rows).
 // Shared-memory rows are 40 bf16 long (80 bytes: the eight rows of an ldmatrix fall into different banks).
 //
 // Needs K % 8 == 0, N even, and 16-byte aligned rows of A and W; everything else goes to the plain kernel.
@@ -16,7 +18,7 @@
 namespace {
 using namespace fzattn;
 
-constexpr int BN = 64, BK = 32, SROW = BK + 8, STAGES = 3, THREADS = 128;
+constexpr int BN = 64, BK = 32, SROW = BK + 8, STAGES = 3;
 
 struct GroupedArgs {
   const __nv_bfloat16* A; long long lda; long long a_group;
@@ -33,11 +35,12 @@ template <> __device__ __forceinline__ void store2<float>(float* p, float a, flo
 template <> __device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16* p, float a, float b) { *(uint32_t*)p = pack_bf16(a, b); }
 
 template <int ROWS, typename TC, bool GLU>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(ROWS == 128 ? 256 : 128)
 grouped_gemm_tc_kernel(const GroupedArgs p) {
   fz_grid_launch_dependents();
   fz_grid_wait();
-  constexpr int WCOLS = ROWS == 64 ? 64 : 16;         // columns a warp owns
+  constexpr int THREADS = ROWS == 128 ? 256 : 128;
+  constexpr int WCOLS = ROWS >= 64 ? 64 : 16;         // columns a warp owns
   constexpr int NB = WCOLS / 8;                       // 8-column blocks per warp
   constexpr int A_BYTES = ROWS * SROW * 2, W_BYTES = BN * SROW * 2, STAGE = A_BYTES + (GLU ? 2 : 1) * W_BYTES;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -103,8 +106,8 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
     acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     if constexpr (GLU) { acu[j][0] = acu[j][1] = acu[j][2] = acu[j][3] = 0.f; }
   }
-  const int wrow = ROWS == 64 ? warp * 16 : 0;        // the warp's first row of the tile
-  const int wcol = ROWS == 64 ? 0 : warp * 16;        // and first column
+  const int wrow = ROWS >= 64 ? warp * 16 : 0;        // the warp's first row of the tile
+  const int wcol = ROWS >= 64 ? 0 : warp * 16;        // and first column
   for (int t = 0; t < ksl; ++t) {
     cp_async_wait<STAGES - 2>();
     __syncthreads();
@@ -162,7 +165,7 @@ int launch(const GroupedArgs& p, dim3 grid, cudaStream_t stream) {
     if (e != cudaSuccess) return (int)e;
     raised = true;
   }
-  fz_launch(kern, grid, dim3(THREADS), smem, stream, p);
+  fz_launch(kern, grid, dim3(ROWS == 128 ? 256 : 128), smem, stream, p);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }
@@ -190,25 +193,27 @@ FZ_API int fz_linear_heads_tc(const void* A, long long lda, long long a_head, co
                               long long c_head, int out_dtype, int M, int H, int N, int K, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || H <= 0) return FZ_OK;
   if (fz_grouped_tc_check(A, lda, a_head, W, C, ldc, c_head, N, K) != FZ_OK) return FZ_BAD_SHAPE;
-  const int rows = M <= 16 ? 16 : 64;
+  const int rows = M <= 16 ? 16 : M >= 256 ? 128 : 64;
   if (H > 65535 || (M + rows - 1) / rows > 65535) return FZ_TOO_LARGE;
   GroupedArgs p = {(const __nv_bfloat16*)A, lda, a_head, (const __nv_bfloat16*)W, (long long)N * K, C, ldc, c_head, M, N, K,
                    nullptr, nullptr, nullptr, 0.f, 0.f, nullptr, 0, 0};
   const dim3 grid((N + BN - 1) / BN, (M + rows - 1) / rows, H);
-  return rows == 16 ? dispatch<16>(p, grid, out_dtype, false, stream) : dispatch<64>(p, grid, out_dtype, false, stream);
+  return rows == 16 ? dispatch<16>(p, grid, out_dtype, false, stream)
+       : rows == 64 ? dispatch<64>(p, grid, out_dtype, false, stream) : dispatch<128>(p, grid, out_dtype, false, stream);
 }
 
-// Experts mode (see fz_grouped_linear). tile_rows: the rows per tile the tile list was built for, 16 or 64.
+// Experts mode (see fz_grouped_linear). tile_rows: the rows per tile the tile list was built for: 16, 64 or 128.
 FZ_API int fz_grouped_linear_tc(const void* A, const void* W, void* C, const int* tiles, int max_tiles, int tile_rows,
                                 const int* a_idx, const int* c_idx, int out_dtype, int N, int K, int glu, float alpha,
                                 float limit, const int* pad_rows, int pad_n, int pad_top, cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0) return FZ_OK;
-  if (fz_grouped_tc_check(A, K, 0, W, C, N, 0, N, K) != FZ_OK || (tile_rows != 16 && tile_rows != 64)) return FZ_BAD_SHAPE;
+  if (fz_grouped_tc_check(A, K, 0, W, C, N, 0, N, K) != FZ_OK || (tile_rows != 16 && tile_rows != 64 && tile_rows != 128)) return FZ_BAD_SHAPE;
   if (max_tiles > 65535) return FZ_TOO_LARGE;
   GroupedArgs p = {(const __nv_bfloat16*)A, K, 0, (const __nv_bfloat16*)W, (long long)(glu ? 2 : 1) * N * K, C, N, 0, 0, N, K,
                    tiles, a_idx, c_idx, alpha, limit, pad_rows, pad_n, pad_top};
   const dim3 grid((N + BN - 1) / BN, max_tiles, 1);
-  return tile_rows == 16 ? dispatch<16>(p, grid, out_dtype, glu != 0, stream) : dispatch<64>(p, grid, out_dtype, glu != 0, stream);
+  return tile_rows == 16 ? dispatch<16>(p, grid, out_dtype, glu != 0, stream)
+       : tile_rows == 64 ? dispatch<64>(p, grid, out_dtype, glu != 0, stream) : dispatch<128>(p, grid, out_dtype, glu != 0, stream);
 }
 
 #ifdef FZ_TIMELINE

@@ -97,6 +97,82 @@ add_rmsnorm_groups_kernel(float* __restrict__ x, const float* __restrict__ delta
   }
 }
 
+// The same for parts whose length is a multiple of 4 and at most 8 * team: a thread keeps two float4 groups of its part
+// in registers (16-byte loads of x, delta and the weights, 16- or 8-byte stores of h), so the row is read once.
+__device__ __forceinline__ float4 ld4(const float* p) { return *(const float4*)p; }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+  const uint2 u = *(const uint2*)p;
+  const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&u.x), b = __bfloat1622float2(*(const __nv_bfloat162*)&u.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4(float* d, float4 v) { *(float4*)d = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* d, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  *(uint2*)d = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
+}
+
+template <typename TW, typename TH>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_groups_vec_kernel(float* __restrict__ x, const float* __restrict__ delta, const TW* __restrict__ w,
+                              TH* __restrict__ h, const int* __restrict__ rows, int n_src, int D, int G, int team,
+                              float eps, int* err) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  __shared__ float warp_ss[8];
+  const int r = blockIdx.x;
+  int src = r;
+  TH* hr = h + (size_t)r * D;
+  if (rows != nullptr) {
+    src = rows[r];
+    if (src < 0 || src >= n_src) {
+      if (src >= n_src && threadIdx.x == 0) atomicOr(err, FZ_ERR_ROW_RANGE);
+      for (int d = threadIdx.x; d < D; d += blockDim.x) hr[d] = Cvt<TH>::from_f(0.f);
+      return;
+    }
+  }
+  float* __restrict__ xr = x + (size_t)src * D;
+  const float* __restrict__ dr = delta ? delta + (size_t)src * D : nullptr;
+  const bool write_x = rows == nullptr && dr != nullptr;
+  const int Dg = D / G;
+  const int teams = blockDim.x / team, t = threadIdx.x / team, lt = threadIdx.x - t * team;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpt = team >> 5;
+  for (int g0 = 0; g0 < G; g0 += teams) {
+    const int g = g0 + t;
+    const int d0 = g * Dg + 4 * lt, d1 = d0 + 4 * team, end = (g + 1) * Dg;
+    const bool in0 = g < G && d0 < end, in1 = g < G && d1 < end;
+    float4 v0 = in0 ? ld4(xr + d0) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 v1 = in1 ? ld4(xr + d1) : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (dr) {
+      const float4 e0 = in0 ? ld4(dr + d0) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 e1 = in1 ? ld4(dr + d1) : make_float4(0.f, 0.f, 0.f, 0.f);
+      v0.x += e0.x; v0.y += e0.y; v0.z += e0.z; v0.w += e0.w;
+      v1.x += e1.x; v1.y += e1.y; v1.z += e1.z; v1.w += e1.w;
+      if (write_x) {
+        if (in0) st4(xr + d0, v0);
+        if (in1) st4(xr + d1, v1);
+      }
+    }
+    float ss = 0.f;
+    ss = fmaf(v0.x, v0.x, ss); ss = fmaf(v0.y, v0.y, ss); ss = fmaf(v0.z, v0.z, ss); ss = fmaf(v0.w, v0.w, ss);
+    ss = fmaf(v1.x, v1.x, ss); ss = fmaf(v1.y, v1.y, ss); ss = fmaf(v1.z, v1.z, ss); ss = fmaf(v1.w, v1.w, ss);
+    ss = warp_sum(ss);
+    __syncthreads();
+    if (lane == 0) warp_ss[warp] = ss;
+    __syncthreads();
+    float total = 0.f;
+    for (int i = 0; i < wpt; ++i) total += warp_ss[t * wpt + i];
+    const float scale = 1.0f / sqrtf(total * (1.0f / (float)Dg) + eps);
+    if (in0) {
+      const float4 g4 = ld4(w + d0);
+      st4(hr + d0, make_float4(g4.x * (v0.x * scale), g4.y * (v0.y * scale), g4.z * (v0.z * scale), g4.w * (v0.w * scale)));
+    }
+    if (in1) {
+      const float4 g4 = ld4(w + d1);
+      st4(hr + d1, make_float4(g4.x * (v1.x * scale), g4.y * (v1.y * scale), g4.z * (v1.z * scale), g4.w * (v1.w * scale)));
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ short convolution
 // seg: (first row, rows, first position, state slot) per portion. state: (slots, taps - 1, C) float32, oldest first.
 template <typename T>
@@ -130,6 +206,64 @@ short_conv_kernel(const T* __restrict__ h, const T* __restrict__ w, const float*
     if (residual) acc += Cvt<T>::to_f(h[(size_t)n * C + c]);
     orow[c] = Cvt<T>::from_f(acc);
   }
+}
+
+// The same with eight channels per thread (16-byte loads of the inputs, the state and the output) for C % 8 == 0.
+__device__ __forceinline__ void ld8(const float* p, float* v) {
+  const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float* v) {
+  const uint4 u = *(const uint4*)p;
+  const __nv_bfloat162* q = (const __nv_bfloat162*)&u;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(q[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void st8(float* p, const float* v) {
+  *(float4*)p = make_float4(v[0], v[1], v[2], v[3]);
+  *(float4*)(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float* v) {
+  uint4 u;
+  __nv_bfloat162* q = (__nv_bfloat162*)&u;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) q[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *(uint4*)p = u;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+short_conv_vec_kernel(const T* __restrict__ h, const T* __restrict__ w, const float* __restrict__ state,
+                      const int* __restrict__ seg, const int* __restrict__ seq_row, T* __restrict__ out, int C, int taps,
+                      int residual) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  const int n = blockIdx.x;
+  const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c0 >= C) return;
+  const int s = seq_row[n];
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (s >= 0) {
+    const int row0 = seg[4 * s], slot = seg[4 * s + 3];
+    const int i = n - row0;
+    const float* st = state != nullptr && slot >= 0 ? state + (size_t)slot * (taps - 1) * C : nullptr;
+    for (int j = 0; j < taps; ++j) {
+      const int k = i - (taps - 1) + j;
+      float v[8];
+      if (k >= 0) ld8(h + (size_t)(row0 + k) * C + c0, v);
+      else if (st != nullptr) ld8(st + (size_t)(taps - 1 + k) * C + c0, v);
+      else continue;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = fmaf(Cvt<T>::to_f(w[(size_t)(c0 + e) * taps + j]), v[e], acc[e]);
+    }
+    if (residual) {
+      float v[8];
+      ld8(h + (size_t)n * C + c0, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += v[e];
+    }
+  }
+  st8(out + (size_t)n * C + c0, acc);
 }
 
 // After the convolution has read the old state: the state of every portion's request becomes its last taps - 1 inputs
@@ -293,8 +427,12 @@ FZ_API int fz_add_rmsnorm_groups(float* x, const float* delta, const void* w, in
   // threads than a part has values
   int team = 256;
   while (team > 32 && (256 / team < G || team > D / G)) team >>= 1;
-#define FZ_GN(TW, TH) do { fz_launch(add_rmsnorm_groups_kernel<TW, TH>, dim3(n_out), dim3(256), 0, stream, x, delta, \
-    (const TW*)w, (TH*)h, rows, n_src, D, G, team, eps, err); FZ_LAUNCH_CHECK(); return FZ_OK; } while (0)
+  // the vectorised kernel: parts of a multiple of 4 values, at most 8 per thread of the team, everything 16-byte aligned
+  const bool vec = (D / G) % 4 == 0 && D / G <= 8 * team && (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)h) & 15) == 0;
+#define FZ_GN(TW, TH) do { \
+    if (vec) fz_launch(add_rmsnorm_groups_vec_kernel<TW, TH>, dim3(n_out), dim3(256), 0, stream, x, delta, (const TW*)w, (TH*)h, rows, n_src, D, G, team, eps, err); \
+    else fz_launch(add_rmsnorm_groups_kernel<TW, TH>, dim3(n_out), dim3(256), 0, stream, x, delta, (const TW*)w, (TH*)h, rows, n_src, D, G, team, eps, err); \
+    FZ_LAUNCH_CHECK(); return FZ_OK; } while (0)
   if (w_dtype == FZ_F32 && h_dtype == FZ_F32) FZ_GN(float, float);
   if (w_dtype == FZ_F32 && h_dtype == FZ_BF16) FZ_GN(float, __nv_bfloat16);
   if (w_dtype == FZ_BF16 && h_dtype == FZ_BF16) FZ_GN(__nv_bfloat16, __nv_bfloat16);
@@ -307,13 +445,17 @@ FZ_API int fz_short_conv(const void* h, const void* w, float* state, const int* 
                          int dtype, int N, int n_seg, int C, int taps, int residual, cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
   if (taps < 1 || taps > MAX_TAPS) return FZ_BAD_SHAPE;
+  const bool vec = C % 8 == 0 && (((uintptr_t)h | (uintptr_t)out | (uintptr_t)state) & 15) == 0;
+  const dim3 vgrid(N, (C / 8 + 127) / 128);
   if (dtype == FZ_F32) {
-    fz_launch(short_conv_kernel<float>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual);
+    if (vec) fz_launch(short_conv_vec_kernel<float>, vgrid, dim3(128), 0, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual);
+    else fz_launch(short_conv_kernel<float>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual);
     FZ_LAUNCH_CHECK();
     if (taps > 1 && state != nullptr && n_seg > 0)
       fz_launch(short_conv_state_kernel<float>, dim3(n_seg, (C + 255) / 256), dim3(256), 0, stream, (const float*)h, state, seg, C, taps);
   } else if (dtype == FZ_BF16) {
-    fz_launch(short_conv_kernel<__nv_bfloat16>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual);
+    if (vec) fz_launch(short_conv_vec_kernel<__nv_bfloat16>, vgrid, dim3(128), 0, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual);
+    else fz_launch(short_conv_kernel<__nv_bfloat16>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual);
     FZ_LAUNCH_CHECK();
     if (taps > 1 && state != nullptr && n_seg > 0)
       fz_launch(short_conv_state_kernel<__nv_bfloat16>, dim3(n_seg, (C + 255) / 256), dim3(256), 0, stream, (const __nv_bfloat16*)h, state, seg, C, taps);

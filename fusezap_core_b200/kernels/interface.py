@@ -106,9 +106,10 @@ class Ops:
         with max(0, p - window + 1) <= j <= p (window 0: 0 <= j <= p), p = meta.pos[n]; out: (N, H, value_width) T."""
         raise NotImplementedError
 
-    def route_by_table(self, token_ids: torch.Tensor, meta: Any, table: torch.Tensor, num_experts: int) -> Any:
+    def route_by_table(self, token_ids: torch.Tensor, meta: Any, table: torch.Tensor, num_experts: int, align: int = 1) -> Any:
         """table: (V, top) int32. Groups the step's (row, choice) pairs by expert table[token_ids[row], choice] (padding
-        rows have none). Returns what `grouped_linear_glu` / `grouped_linear_scatter` need, valid until the next call."""
+        rows have none). Returns what `grouped_linear_glu` / `grouped_linear_scatter` need, valid until the next call.
+        align: a common divisor of the sizes of the products that will use the route (a hint for the choice of tiles)."""
         raise NotImplementedError
 
     def grouped_linear_glu(self, h: torch.Tensor, w: torch.Tensor, route: Any, y: torch.Tensor, alpha: float,

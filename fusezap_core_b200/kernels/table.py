@@ -725,7 +725,7 @@ class CudaOps(Ops):
             "latent_attention", nbytes)
 
     # ---- experts chosen by a table
-    def route_by_table(self, token_ids, meta, table, num_experts):
+    def route_by_table(self, token_ids, meta, table, num_experts, align: int = 1):
         self._want(token_ids, "token ids", (torch.int32,), 1)
         self._want(table, "expert table", (torch.int32,), 2)
         n, top = token_ids.shape[0], table.shape[1]
@@ -733,6 +733,8 @@ class CudaOps(Ops):
         tile = int(self.mix.fz_grouped_tile_rows())
         if self.use_tensor_cores and self.grouped_tensor_cores and n * top <= 16 * num_experts:
             tile = 16
+        elif self.use_tensor_cores and self.grouped_tensor_cores and align % 8 == 0 and n * top >= 192 * num_experts:
+            tile = 128      # (only where the sizes are sure to go to the tensor-core kernels: the plain ones take 64 at most)
         max_tiles = -(-n * top // tile) + min(num_experts, n * top)
         idx = self._scratch("expert route", 2 * n * top + 3 * max_tiles, torch.int32)
         a_idx, c_idx, tiles = idx[:n * top], idx[n * top: 2 * n * top], idx[2 * n * top: 2 * n * top + 3 * max_tiles]
@@ -761,7 +763,7 @@ class CudaOps(Ops):
                                                          c_float(alpha), c_float(limit), c_void_p(0), c_int(0), c_int(0),
                                                          self._stream()), "grouped_linear_glu (tensor cores)", nbytes)
             return
-        self._check(self.mix.fz_grouped_linear(_p(h), _p(w), _p(y), _p(tiles), c_int(max_tiles), _p(a_idx), c_void_p(0),
+        self._check(self.mix.fz_grouped_linear(_p(h), _p(w), _p(y), _p(tiles), c_int(max_tiles), c_int(tile), _p(a_idx), c_void_p(0),
                                                c_int(_CODE[self.dtype]), c_int(_CODE[self.dtype]), c_int(inter), c_int(k),
                                                c_int(1), c_float(alpha), c_float(limit), c_void_p(0), c_int(0), c_int(0),
                                                self._stream()),
@@ -782,7 +784,7 @@ class CudaOps(Ops):
                                                          c_int(0), c_float(0.0), c_float(0.0), _p(seq_row), c_int(n), c_int(top),
                                                          self._stream()), "grouped_linear_scatter (tensor cores)", nbytes)
             return
-        self._check(self.mix.fz_grouped_linear(_p(y), _p(w), _p(out), _p(tiles), c_int(max_tiles), c_void_p(0), _p(c_idx),
+        self._check(self.mix.fz_grouped_linear(_p(y), _p(w), _p(out), _p(tiles), c_int(max_tiles), c_int(tile), c_void_p(0), _p(c_idx),
                                                c_int(_CODE[self.dtype]), c_int(_CODE[torch.float32]), c_int(d), c_int(inter),
                                                c_int(0), c_float(0.0), c_float(0.0), _p(seq_row), c_int(n), c_int(top),
                                                self._stream()),

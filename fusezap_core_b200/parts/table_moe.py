@@ -9,6 +9,8 @@ The sum over a row's experts is left to the block (returned as `(terms, top, 1 /
 together with its own terms.
 """
 from __future__ import annotations
+import math
+
 import torch
 
 from ..weights import ParamSpec
@@ -53,7 +55,7 @@ class TableMoE(FeedForward):
 
     def forward(self, ctx, h: torch.Tensor):
         n, ops, ws = h.shape[0], ctx.ops, ctx.ws
-        route = ops.route_by_table(ctx.token_ids, ctx.meta, self.table, self.E)
+        route = ops.route_by_table(ctx.token_ids, ctx.meta, self.table, self.E, math.gcd(self.D, self.I))
         y = ws.get("moe_act", (n * self.top, self.I), ops.dtype)             # rows in the sorted order of the pairs
         ops.grouped_linear_glu(h, self.w_gate_up, route, y, self.alpha, self.limit)
         terms = ws.get("moe_terms", (n * self.top, self.D), torch.float32)   # row n * top + k: the k-th expert of row n

@@ -240,7 +240,7 @@ class PlainOpsWide(PlainOps):
             w = torch.softmax((q[i].float() @ e.T) * scale, -1)    # (H, keys)
             out[i] = (w @ e[:, :value_width]).to(out.dtype)
 
-    def route_by_table(self, token_ids, meta, table, num_experts):
+    def route_by_table(self, token_ids, meta, table, num_experts, align=1):
         ex = table[token_ids.long().clamp(0, table.shape[0] - 1)].long()
         assert ((ex >= 0) & (ex < num_experts)).all()
         return ex, meta.seq_row >= 0
