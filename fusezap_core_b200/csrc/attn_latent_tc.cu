@@ -310,8 +310,12 @@ attn_latent_merge_kernel(const float* __restrict__ part_o, const float* __restri
   __syncthreads();
   for (int c = threadIdx.x; c < Wv; c += blockDim.x) {
     float acc = 0.f;
-    for (int y = 0; y < n_split; ++y)
-      if (w_s[y] > 0.f) acc = fmaf(part_o[((base + y) * BM + r) * Wv + c], w_s[y], acc);
+#pragma unroll 8
+    for (int y = 0; y < n_split; ++y) {      // independent loads: an empty range (weight 0) is not read
+      const float wy = w_s[y];
+      const float v = wy > 0.f ? part_o[((base + y) * BM + r) * Wv + c] : 0.f;
+      acc = fmaf(v, wy, acc);
+    }
     out[((size_t)row0 * H + pair0 + r) * Wv + c] = __float2bfloat16_rn(acc * inv_s);
   }
 }

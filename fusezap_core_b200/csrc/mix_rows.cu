@@ -231,7 +231,9 @@ __device__ __forceinline__ void st8(__nv_bfloat16* p, const float* v) {
   *(uint4*)p = u;
 }
 
-template <typename T>
+// TAPS > 0: the tap count is known at compile time and the thread's 8 x TAPS weights (contiguous in the (C, taps)
+// matrix) come in as TAPS 16-byte groups (bfloat16) instead of one by one; TAPS == 0: any tap count.
+template <typename T, int TAPS>
 __global__ void __launch_bounds__(128)
 short_conv_vec_kernel(const T* __restrict__ h, const T* __restrict__ w, const float* __restrict__ state,
                       const int* __restrict__ seg, const int* __restrict__ seq_row, T* __restrict__ out, int C, int taps,
@@ -247,14 +249,30 @@ short_conv_vec_kernel(const T* __restrict__ h, const T* __restrict__ w, const fl
     const int row0 = seg[4 * s], slot = seg[4 * s + 3];
     const int i = n - row0;
     const float* st = state != nullptr && slot >= 0 ? state + (size_t)slot * (taps - 1) * C : nullptr;
-    for (int j = 0; j < taps; ++j) {
-      const int k = i - (taps - 1) + j;
-      float v[8];
-      if (k >= 0) ld8(h + (size_t)(row0 + k) * C + c0, v);
-      else if (st != nullptr) ld8(st + (size_t)(taps - 1 + k) * C + c0, v);
-      else continue;
+    if constexpr (TAPS > 0) {
+      float wv[8 * TAPS];                  // wv[e * TAPS + j]: tap j of channel c0 + e
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = fmaf(Cvt<T>::to_f(w[(size_t)(c0 + e) * taps + j]), v[e], acc[e]);
+      for (int m = 0; m < TAPS; ++m) ld8(w + (size_t)c0 * TAPS + 8 * m, wv + 8 * m);
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) {
+        const int k = i - (TAPS - 1) + j;
+        float v[8];
+        if (k >= 0) ld8(h + (size_t)(row0 + k) * C + c0, v);
+        else if (st != nullptr) ld8(st + (size_t)(TAPS - 1 + k) * C + c0, v);
+        else continue;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(wv[e * TAPS + j], v[e], acc[e]);
+      }
+    } else {
+      for (int j = 0; j < taps; ++j) {
+        const int k = i - (taps - 1) + j;
+        float v[8];
+        if (k >= 0) ld8(h + (size_t)(row0 + k) * C + c0, v);
+        else if (st != nullptr) ld8(st + (size_t)(taps - 1 + k) * C + c0, v);
+        else continue;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(Cvt<T>::to_f(w[(size_t)(c0 + e) * taps + j]), v[e], acc[e]);
+      }
     }
     if (residual) {
       float v[8];
@@ -416,6 +434,19 @@ rotate_heads_kernel(const T* __restrict__ q, int W, int off, const float* __rest
     out[((size_t)n * H + hh) * Wo + out_off + d] = Cvt<T>::from_f(v);
   }
 }
+template <typename T>
+void launch_conv_vec(dim3 grid, cudaStream_t stream, const T* h, const T* w, const float* state, const int* seg,
+                     const int* seq_row, T* out, int C, int taps, int residual) {
+  const bool w_ok = ((uintptr_t)w & 15) == 0;       // the grouped weight loads want 16-byte aligned rows of 8 x taps values
+#define FZ_CV(N) fz_launch(short_conv_vec_kernel<T, N>, grid, dim3(128), 0, stream, h, w, state, seg, seq_row, out, C, taps, residual)
+  if (w_ok && taps == 2) FZ_CV(2);
+  else if (w_ok && taps == 3) FZ_CV(3);
+  else if (w_ok && taps == 4) FZ_CV(4);
+  else if (w_ok && taps == 5) FZ_CV(5);
+  else if (w_ok && taps == 8) FZ_CV(8);
+  else FZ_CV(0);
+#undef FZ_CV
+}
 }  // namespace
 
 FZ_API int fz_add_rmsnorm_groups(float* x, const float* delta, const void* w, int w_dtype, void* h, int h_dtype,
@@ -448,13 +479,13 @@ FZ_API int fz_short_conv(const void* h, const void* w, float* state, const int* 
   const bool vec = C % 8 == 0 && (((uintptr_t)h | (uintptr_t)out | (uintptr_t)state) & 15) == 0;
   const dim3 vgrid(N, (C / 8 + 127) / 128);
   if (dtype == FZ_F32) {
-    if (vec) fz_launch(short_conv_vec_kernel<float>, vgrid, dim3(128), 0, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual);
+    if (vec) launch_conv_vec<float>(vgrid, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual);
     else fz_launch(short_conv_kernel<float>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual);
     FZ_LAUNCH_CHECK();
     if (taps > 1 && state != nullptr && n_seg > 0)
       fz_launch(short_conv_state_kernel<float>, dim3(n_seg, (C + 255) / 256), dim3(256), 0, stream, (const float*)h, state, seg, C, taps);
   } else if (dtype == FZ_BF16) {
-    if (vec) fz_launch(short_conv_vec_kernel<__nv_bfloat16>, vgrid, dim3(128), 0, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual);
+    if (vec) launch_conv_vec<__nv_bfloat16>(vgrid, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual);
     else fz_launch(short_conv_kernel<__nv_bfloat16>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual);
     FZ_LAUNCH_CHECK();
     if (taps > 1 && state != nullptr && n_seg > 0)
