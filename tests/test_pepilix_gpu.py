@@ -296,6 +296,7 @@ def test_table_routed_experts(dtype, E, top, K, I, D, N, tensor_cores):
     if dtype == "float32" and not tensor_cores:
         pytest.skip("the float32 path has the plain kernels only")
     ops.grouped_tensor_cores = tensor_cores
+    ops.grouped_tiles_128 = N >= 400        # the large row tiles are an option of the table: exercised here
     V, limit = 31, 0.8
     h = torch.randn(N, K, generator=g).to(dt)
     wgu = (torch.randn(E, 2 * I, K, generator=g) * 0.12).to(dt)
@@ -310,7 +311,7 @@ def test_table_routed_experts(dtype, E, top, K, I, D, N, tensor_cores):
     ops.grouped_linear_glu(h.to(DEV), wgu.to(DEV), route, y, 1.702, limit)
     terms = torch.full((N * top, D), float("nan"), device=DEV)
     ops.grouped_linear_scatter(y, wd.to(DEV), route, terms)
-    ops.grouped_tensor_cores = True
+    ops.grouped_tensor_cores, ops.grouped_tiles_128 = True, False
     ops.check_errors()
     rnd = (lambda t: t) if dtype == "float32" else (lambda t: t.to(torch.bfloat16).to(F))
     tol = 2e-5 if dtype == "float32" else 2.0 ** -6
