@@ -409,3 +409,57 @@ def test_command_line_generates_from_a_preset_with_random_weights(capsys):
     lines = [json.loads(x) for x in capsys.readouterr().out.splitlines() if x.startswith("{")]
     assert [o["num_prompt_tokens"] for o in lines] == [5, 40, 1]
     assert all(len(o["token_ids"]) == 6 and o["finish_reason"] == "length" for o in lines)
+
+
+def _random_config(seed: int) -> dict:
+    """A configuration drawn from a seed: odd and even sizes, any order of layers that own or borrow a cache, layers
+    without feed-forward, one to several norm groups and taps."""
+    rng = np.random.default_rng(seed)
+    groups = int(rng.choice([1, 2, 3, 5]))
+    width = groups * int(rng.integers(5, 40))
+    taps = int(rng.integers(1, 7))
+    vocab = int(rng.integers(20, 300))
+    kinds = []
+    for _ in range(int(rng.integers(1, 3))):      # one or two kinds of mixer sizes; layers borrow only from their own kind
+        rot = 2 * int(rng.integers(1, 9))
+        kinds.append(dict(heads=int(rng.integers(1, 10)), dim=int(rng.integers(1, 40)), rot_dim=rot + int(rng.choice([0, 0, 3])),
+                          vdim=int(rng.integers(1, 40)), kv_rank=int(rng.integers(3, 70)), scale=float(rng.uniform(0.05, 0.4)),
+                          rot={"base": float(rng.choice([100.0, 10000.0, 500000.0])), "dims": rot}))
+    layers, owners = [], {}
+    for i in range(int(rng.integers(1, 6))):
+        k = int(rng.integers(0, len(kinds)))
+        m = dict(kinds[k])
+        m["heads"], m["dim"], m["vdim"] = int(rng.integers(1, 10)), int(rng.integers(1, 40)), int(rng.integers(1, 40))
+        if k in owners and rng.random() < 0.5:
+            m["kv_from"] = int(rng.choice(owners[k]))
+        else:
+            owners.setdefault(k, []).append(i)
+        mlp = None
+        if rng.random() < 0.8:
+            experts = int(rng.integers(1, 9))
+            mlp = {"kind": "moe", "router": {"experts": experts, "top": int(rng.integers(1, experts + 1))},
+                   "expert": {"ff": int(rng.integers(1, 50)), "limit": float(rng.uniform(0.3, 3.0))}}
+        layers.append({"type": "latent_attention", "mixer": m, "mlp": mlp})
+    return {"architecture": "Pepilix", "vocab": vocab, "width": width, "embedding": {"scale": float(rng.uniform(0.5, 20))},
+            "logit_scale": float(rng.uniform(0.2, 2.0)), "norm": {"eps": float(rng.choice([1e-6, 1e-5, 1e-3])), "groups": groups},
+            "canon": {"taps": taps}, "layers": layers}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(tmp_path, seed, dtype):
+    """Whatever sizes a configuration gives (odd ones included, which take the general kernels), portions and single
+    tokens through the engine equal the plain model on the whole sequence."""
+    from fusezap_core_b200.weights import write_random_model
+    from safetensors.torch import load_file
+    import os
+    cfg = _random_config(seed)
+    d = write_random_model(cfg, str(tmp_path / "m"), 100 + seed, "float32", norm_noise=True, std_scale=4.0)
+    w = load_file(os.path.join(d, "model.safetensors"))
+    model, cache, runner = engine_parts(d, dtype, page=16, pages=12, slots=2, max_len=192)
+    toks = tokens_for(cfg, (150,), seed=seed)[0]
+    ref = plain_pepilix.forward(cfg, w, toks, rounded=dtype == "bfloat16").numpy()
+    for cuts in ([150], [9, 1, 2, 33, 1, 1, 64]):
+        got = run_cut(runner, cache, "r", toks, cuts)
+        assert rel_rms(got, ref) < LIMIT[dtype], f"seed {seed}: {cfg}"
+    model.ops.check_errors()
