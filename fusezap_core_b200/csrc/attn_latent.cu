@@ -23,12 +23,12 @@ template <typename T, int DPL>   // DPL: output values per lane = ceil(Wv / 32)
 __global__ void attn_latent_kernel(const T* __restrict__ q, const T* __restrict__ pool, const int* __restrict__ pos,
                                    const int* __restrict__ seq_row, const int* __restrict__ table, int mb,
                                    long long page_stride, int page_size, int num_pages, T* __restrict__ out, int H, int W,
-                                   int Wv, float scale, int window, int* err) {
+                                   int Wv, float scale, int window, int slice, int* err) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   extern __shared__ float smem[];
-  const int n = blockIdx.x, h0 = blockIdx.y * MAX_SLICE;
-  const int G = min(MAX_SLICE, H - h0);
+  const int n = blockIdx.x, h0 = blockIdx.y * slice;      // `slice` heads per block (at most MAX_SLICE)
+  const int G = min(slice, H - h0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, NW = blockDim.x >> 5;
   const int kstride = W + 1;
   float* Ks = smem;                       // [CHUNK][W + 1]
@@ -112,7 +112,9 @@ template <typename T, int DPL>
 int launch(const void* q, const void* pool, const int* pos, const int* seq_row, const int* table, int mb,
            long long page_stride, int page_size, int num_pages, void* out, int N, int H, int W, int Wv, float scale,
            int window, int* err, cudaStream_t stream) {
-  const int G = H < MAX_SLICE ? H : MAX_SLICE;
+  // heads per block: as many as share a chunk of keys in shared memory (fewer for very wide cached vectors)
+  int G = H < MAX_SLICE ? H : MAX_SLICE;
+  while (G > 1 && sizeof(float) * ((size_t)CHUNK * (W + 1) + (size_t)G * W) > 200 * 1024) G = (G + 1) / 2;
   const int NW = G < MAX_WARPS ? G : MAX_WARPS;
   const size_t smem = sizeof(float) * ((size_t)CHUNK * (W + 1) + (size_t)G * W);
   auto kern = attn_latent_kernel<T, DPL>;
@@ -123,8 +125,8 @@ int launch(const void* q, const void* pool, const int* pos, const int* seq_row, 
     if (e != cudaSuccess) return (int)e;
     allowed = smem;
   }
-  fz_launch(kern, dim3(N, (H + MAX_SLICE - 1) / MAX_SLICE), dim3(32 * NW), smem, stream, (const T*)q, (const T*)pool, pos,
-            seq_row, table, mb, page_stride, page_size, num_pages, (T*)out, H, W, Wv, scale, window, err);
+  fz_launch(kern, dim3(N, (H + G - 1) / G), dim3(32 * NW), smem, stream, (const T*)q, (const T*)pool, pos,
+            seq_row, table, mb, page_stride, page_size, num_pages, (T*)out, H, W, Wv, scale, window, G, err);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }
@@ -148,7 +150,7 @@ int dispatch(const void* q, const void* pool, const int* pos, const int* seq_row
 // Sizes taken: any number of heads, 0 < Wv <= W, W <= 1024, Wv <= 512.
 FZ_API int fz_attn_latent_check(int H, int W, int Wv) {
   if (H <= 0 || W <= 0 || Wv <= 0 || Wv > W || W > MAX_W || Wv > MAX_WV) return FZ_BAD_SHAPE;
-  if ((H + MAX_SLICE - 1) / MAX_SLICE > 65535) return FZ_BAD_SHAPE;
+  if (H > 65535) return FZ_BAD_SHAPE;
   return FZ_OK;
 }
 

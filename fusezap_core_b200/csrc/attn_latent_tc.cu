@@ -278,7 +278,7 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
 // Adds up a tile's key ranges: out = sum_y o_y 2^(m_y - m) / sum_y l_y 2^(m_y - m), m = max_y m_y.
 // One block per (tile, pair): a warp turns the ranges' (max, sum) into weights once, then every thread adds up its
 // columns with independent loads. n_split <= 32.
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 attn_latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ seg,
                          int n_seg, int n_split, __nv_bfloat16* __restrict__ out, int H, int Wv) {
   fz_grid_launch_dependents();
@@ -304,18 +304,19 @@ attn_latent_merge_kernel(const float* __restrict__ part_o, const float* __restri
       const float up = __shfl_up_sync(0xffffffffu, l, o);
       if (y >= o) l += up;
     }
-    w_s[y] = w;
+    w_s[y] = w;                                            // (0 for the lanes beyond the ranges)
     if (y == 31) inv_s = 1.0f / l;
   }
   __syncthreads();
   for (int c = threadIdx.x; c < Wv; c += blockDim.x) {
+    // all ranges' loads are issued before any is used (the loop has a constant bound and is unrolled); an empty range
+    // (weight 0) is not read
+    float v[32];
+#pragma unroll
+    for (int y = 0; y < 32; ++y) v[y] = (y < n_split && w_s[y] > 0.f) ? part_o[((base + y) * BM + r) * Wv + c] : 0.f;
     float acc = 0.f;
-#pragma unroll 8
-    for (int y = 0; y < n_split; ++y) {      // independent loads: an empty range (weight 0) is not read
-      const float wy = w_s[y];
-      const float v = wy > 0.f ? part_o[((base + y) * BM + r) * Wv + c] : 0.f;
-      acc = fmaf(v, wy, acc);
-    }
+#pragma unroll
+    for (int y = 0; y < 32; ++y) acc = fmaf(v[y], w_s[y < n_split ? y : 0], acc);
     out[((size_t)row0 * H + pair0 + r) * Wv + c] = __float2bfloat16_rn(acc * inv_s);
   }
 }
@@ -350,7 +351,7 @@ int launch(const void* q, const void* pool, const int* seg, int n_seg, const int
             window, part_o, part_ml, split_keys, err);
   FZ_LAUNCH_CHECK();
   if (split_keys > 0) {
-    fz_launch(attn_latent_merge_kernel, dim3(blocks, BM), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, seg,
+    fz_launch(attn_latent_merge_kernel, dim3(blocks, BM), dim3(256), 0, stream, (const float*)part_o, (const float*)part_ml, seg,
               n_seg, n_split, (__nv_bfloat16*)out, H, Wv);
     FZ_LAUNCH_CHECK();
   }

@@ -194,7 +194,8 @@ def _attention_reference(q, entries, Wv, scale, lo, p):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,W,Wv,page", [(6, 160, 128, 16), (40, 22, 16, 4), (1, 104, 72, 8), (3, 48, 40, 64),
-                                         (16, 576, 512, 16), (5, 64, 32, 8), (20, 96, 80, 4), (70, 32, 32, 16)])
+                                         (16, 576, 512, 16), (5, 64, 32, 8), (20, 96, 80, 4), (70, 32, 32, 16),
+                                         (33, 1000, 500, 16)])
 def test_latent_attention_rows_of_any_portion(dtype, H, W, Wv, page):
     """Two requests on shuffled pages: a long portion behind a prefix, single tokens, and a padding row, against the
     plain softmax over each row's own keys."""
