@@ -1,7 +1,7 @@
 """Benchmark: decode tokens per second of the Llama-3.1-8B-sized model (random bf16 weights) on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L] [--impl ours|reference]
-                    [--preset NAME] [--workload decode|stream]
+                    [--preset NAME] [--workload decode|stream|pepilix]
 
 A "step" is one decode step of `--batch` requests whose contexts end at `--context` tokens. Prints ONE JSON line:
   value      decoded tokens per second, timed on the device (CUDA events around K steps: metadata copy + graph replay)
@@ -22,6 +22,11 @@ Weights are N(0, 0.02) drawn on the device, prompts are seeded uniform token ids
 with prompt lengths uniform in [16, 1024] and 256 new tokens each, one arriving per engine step, through
 `LLMEngine.add_request` / `step()`; the line's value is generated tokens per second of wall clock from the first
 arrival to the last token.
+
+`--workload pepilix` (`--sizes w1024,w2048`, `--layers 4`) times the Pepilix design beside the dense decoder at equal
+width, layers, heads, vocabulary and active feed-forward size: a 2,048-token prompt and decode steps at `--batch`
+requests through `LLMEngine.step()`, and (unless `--no-points`) a kernel-by-kernel profile of both; its line's `sizes`
+holds the numbers, `value` is Pepilix's decode tokens per second at the first size.
 """
 from __future__ import annotations
 import argparse
