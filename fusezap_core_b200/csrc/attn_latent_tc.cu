@@ -134,6 +134,9 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
   const int r_lo = rg * 16 + (lane >> 2);                        // this thread's pairs: r_lo and r_lo + 8
   const int qp[2] = {pos0 + (pair0 + r_lo) / H, pos0 + (pair0 + r_lo + 8) / H};
   const int ksteps = W / 16;
+  // A pair group none of whose 16 pairs exists (a decoded token with few heads, a portion's last tile) takes part in the
+  // loads and the barriers only: its products are skipped (the decision is the same for all lanes of a warp).
+  const bool active = rg * 16 < valid;
 
   for (int t = 0; t < ntiles; ++t) {
     if (t + 1 < ntiles) { issue(t + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
@@ -157,13 +160,15 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
         mma_bf16(acc[2 * jb + 1], qf, kf[2], kf[3]);
       }
     };
-    int ks = 0;
+    if (active) {
+      int ks = 0;
 #pragma unroll 2
-    for (; ks + 1 < ksteps; ks += 2) {
-      k_step(ks, s);
-      k_step(ks + 1, s2);
+      for (; ks + 1 < ksteps; ks += 2) {
+        k_step(ks, s);
+        k_step(ks + 1, s2);
+      }
+      if (ks < ksteps) k_step(ks, s);
     }
-    if (ks < ksteps) k_step(ks, s);
 #pragma unroll
     for (int j = 0; j < NBS; ++j) { s[j][0] += s2[j][0]; s[j][1] += s2[j][1]; s[j][2] += s2[j][2]; s[j][3] += s2[j][3]; }
     float mx[2] = {-INFINITY, -INFINITY};
@@ -216,7 +221,7 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
     __syncthreads();
     const int vchunk0 = half * NV16 * 2;                         // this warp's first value chunk (8 columns each)
 #pragma unroll
-    for (int kk = 0; kk < BN / 16; ++kk) {
+    for (int kk = 0; kk < (active ? BN / 16 : 0); ++kk) {
       uint32_t pf[4];
       ldmatrix_x4(pf, at(s_p, rg * 16 + (lane & 15), kk * 2 + (lane >> 4), pstride));
 #pragma unroll

@@ -4,12 +4,13 @@
 // kernels of grouped_gemm.cu; a row's result does not depend on the tile it lands in (every output is the sum over k in
 // the fixed order of the 16-wide MMA steps).
 //
-// A block computes ROWS x 64 outputs, k in slices of 32 through a three-stage cp.async ring. ROWS = 64 (four warps) or
+// A block computes ROWS x 64 outputs, k in slices of 32 (64 for the 16-row tiles) through a three-stage cp.async ring. ROWS = 64 (four warps) or
 // 128 (eight): warp w owns rows 16 w .. 16 w + 15 and all 64 columns (many rows per group: prompts; with 64 x 64 tiles
 // the products of a 2,048-token step draw their operands from L2 at about 5 TB/s and are bound by that, so groups with
 // hundreds of rows take 128). ROWS = 16: each of four warps owns the 16 rows and 16 of the columns (few rows per group:
 // decoded tokens, where the weights are read once whatever the rows).
-// Shared-memory rows are 40 bf16 long (80 bytes: the eight rows of an ldmatrix fall into different banks).
+// Shared-memory rows are 16 bytes longer than a slice (80 or 144 bytes: the eight rows of an ldmatrix fall into
+// different banks).
 //
 // Needs K % 8 == 0, N even, and 16-byte aligned rows of A and W; everything else goes to the plain kernel.
 #include "attn_mma.cuh"
@@ -18,7 +19,14 @@
 namespace {
 using namespace fzattn;
 
-constexpr int BN = 64, BK = 32, SROW = BK + 8, STAGES = 3;
+constexpr int BN = 64, STAGES = 3;
+// k per slice: 32 for the many-row tiles, 64 for the 16-row tiles (measured at width 2,048: the few-row products of a
+// decode step 42 -> 34 us and 23 -> 18 us with 64, the many-row products of a prompt 319 -> 350 us)
+template <int ROWS> struct Slice {
+  static constexpr int BK = ROWS == 16 ? 64 : 32;
+  static constexpr int SROW = BK + 8;       // shared-memory row: 16 bytes more than the slice, so ldmatrix rows spread over the banks
+  static constexpr int CH = BK / 8;         // 16-byte chunks per row of a slice
+};
 
 struct GroupedArgs {
   const __nv_bfloat16* A; long long lda; long long a_group;
@@ -40,6 +48,7 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   constexpr int THREADS = ROWS == 128 ? 256 : 128;
+  constexpr int BK = Slice<ROWS>::BK, SROW = Slice<ROWS>::SROW, CH = Slice<ROWS>::CH;
   constexpr int WCOLS = ROWS >= 64 ? 64 : 16;         // columns a warp owns
   constexpr int NB = WCOLS / 8;                       // 8-column blocks per warp
   constexpr int A_BYTES = ROWS * SROW * 2, W_BYTES = BN * SROW * 2, STAGE = A_BYTES + (GLU ? 2 : 1) * W_BYTES;
@@ -80,15 +89,15 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
   auto issue = [&](int t) {
     const uint32_t st = s0 + (t % STAGES) * STAGE;
     const int k0 = t * BK;
-    // A: ROWS rows x 4 chunks of 8; W (and the up rows): 64 rows x 4 chunks
-    for (int e = tid; e < ROWS * 4; e += THREADS) {
-      const int r = e >> 2, c = e & 3;
+    // A: ROWS rows x CH chunks of 8; W (and the up rows): 64 rows x CH chunks
+    for (int e = tid; e < ROWS * CH; e += THREADS) {
+      const int r = e / CH, c = e % CH;
       const int ar = arow_s[r];
       const bool ok = ar >= 0 && k0 + c * 8 < K;
       cp_async16(st + r * SROW * 2 + c * 16, ok ? A + (long long)ar * p.lda + k0 + c * 8 : A, ok);
     }
-    for (int e = tid; e < BN * 4; e += THREADS) {
-      const int r = e >> 2, c = e & 3;
+    for (int e = tid; e < BN * CH; e += THREADS) {
+      const int r = e / CH, c = e % CH;
       const bool ok = n0 + r < N && k0 + c * 8 < K;
       const __nv_bfloat16* src = W + (long long)(n0 + r) * K + k0 + c * 8;
       cp_async16(st + A_BYTES + r * SROW * 2 + c * 16, ok ? src : W, ok);
@@ -157,6 +166,7 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
 
 template <int ROWS, typename TC, bool GLU>
 int launch(const GroupedArgs& p, dim3 grid, cudaStream_t stream) {
+  constexpr int SROW = Slice<ROWS>::SROW;
   constexpr size_t smem = (size_t)STAGES * (ROWS * SROW * 2 + (GLU ? 2 : 1) * BN * SROW * 2);
   auto kern = grouped_gemm_tc_kernel<ROWS, TC, GLU>;
   static bool raised = false;
