@@ -140,3 +140,29 @@ def test_state_slots_take_the_dtype_the_mixer_declares():
     cm.free("a")
     cm.ensure("b", 3)
     assert cm.state_slot("b") == slot and int(t[(1, "count")][slot].sum()) == 0, "a slot is zeroed when it is handed out"
+
+
+def test_latent_need_has_one_vector_per_token_and_shares_the_page_bookkeeping():
+    """A `LatentNeed` group allocates (slots, pages, page_size, width), hands a mixer that pool as its keys and no
+    values, and gives back, reuses and windows pages exactly like a `KVNeed` group."""
+    import torch
+    from fusezap_core_b200.cache import CacheManager, KVNeed, LatentNeed
+    cm = CacheManager({0: LatentNeed(40), 2: LatentNeed(40), 1: KVNeed(2, 16), 3: LatentNeed(24, window=6)}, {(0, "conv"): (2, 8)},
+                      page_size=4, num_pages=10, max_requests=2, max_model_len=40, dtype=torch.float32, device="cpu")
+    by_need = {g.need: g for g in cm.groups}
+    assert tuple(by_need[LatentNeed(40)].pool.shape) == (2, 10, 4, 40) and by_need[LatentNeed(40)].slots == [0, 2]
+    assert tuple(by_need[KVNeed(2, 16)].pool.shape) == (1, 10, 2, 2, 4, 16)
+    keys, values = cm.groups[cm.slot_group[2]].view(2)
+    assert tuple(keys.shape) == (10, 4, 40) and values is None
+    cm.ensure("a", 13)
+    cm.commit("a", 13)
+    win = cm.slot_group[3]
+    assert cm.table(cm.slot_group[0], "a") == [0, 1, 2, 3] and cm.table(win, "a") == [-1, -1, 2, 3]      # positions 8.. live
+    cm.ensure("b", 9)
+    cm.commit("b", 9)
+    first = cm.table(cm.slot_group[0], "a")
+    cm.free("a")
+    cm.ensure("c", 5)
+    assert cm.table(cm.slot_group[0], "c") == first[:2][::-1] or set(cm.table(cm.slot_group[0], "c")) <= set(first)
+    assert cm.state_slot("c") == 0 and cm.state_slot("b") == 1
+    cm.check()
