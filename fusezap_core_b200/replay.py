@@ -48,7 +48,8 @@ def main(argv=None) -> int:
         if not line:
             continue
         step = json.loads(line)
-        portions = [Portion(e["id"], e["tokens"], e.get("want", [])) for e in step.get("entries", [])]
+        # (an entry that brings no tokens has nothing to run)
+        portions = [Portion(e["id"], e["tokens"], e.get("want", [])) for e in step.get("entries", []) if e.get("tokens")]
         if portions:
             logits = runner.run(portions)
             if logits.shape[0]:
