@@ -5,10 +5,11 @@
 // the fixed order of the 16-wide MMA steps).
 //
 // A block computes ROWS x 64 outputs, k in slices of 32 (64 for the 16-row tiles) through a three-stage cp.async ring. ROWS = 64 (four warps) or
-// 128 (eight): warp w owns rows 16 w .. 16 w + 15 and all 64 columns (many rows per group: prompts; with 64 x 64 tiles
-// the products of a 2,048-token step draw their operands from L2 at about 5 TB/s and are bound by that, so groups with
-// hundreds of rows take 128). ROWS = 16: each of four warps owns the 16 rows and 16 of the columns (few rows per group:
-// decoded tokens, where the weights are read once whatever the rows).
+// 128 (eight): warp w owns 32 rows (32 (w / 2) ..) and 32 columns (32 (w % 2) ..), so a 16-wide k step takes two
+// ldmatrix of A and two of W for eight MMAs (a warp that owned 16 rows and all 64 columns took one and four: the
+// shared-memory pipe, not the tensor pipe, was the busier one). Many rows per group: prompts. ROWS = 16: each of four
+// warps owns the 16 rows and 16 of the columns (few rows per group: decoded tokens, where the weights are read once
+// whatever the rows).
 // Shared-memory rows are 16 bytes longer than a slice (80 or 144 bytes: the eight rows of an ldmatrix fall into
 // different banks).
 //
@@ -49,8 +50,9 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
   fz_grid_wait();
   constexpr int THREADS = ROWS == 128 ? 256 : 128;
   constexpr int BK = Slice<ROWS>::BK, SROW = Slice<ROWS>::SROW, CH = Slice<ROWS>::CH;
-  constexpr int WCOLS = ROWS >= 64 ? 64 : 16;         // columns a warp owns
+  constexpr int WCOLS = ROWS >= 64 ? 32 : 16;         // columns a warp owns
   constexpr int NB = WCOLS / 8;                       // 8-column blocks per warp
+  constexpr int MB = ROWS >= 64 ? 2 : 1;              // 16-row blocks per warp
   constexpr int A_BYTES = ROWS * SROW * 2, W_BYTES = BN * SROW * 2, STAGE = A_BYTES + (GLU ? 2 : 1) * W_BYTES;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int arow_s[ROWS], crow_s[ROWS];
@@ -109,14 +111,16 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
   for (int t = 0; t < STAGES - 1; ++t) {
     if (t < ksl) issue(t); else cp_async_commit();
   }
-  float acc[NB][4], acu[GLU ? NB : 1][4];
+  float acc[MB][NB][4], acu[GLU ? MB : 1][GLU ? NB : 1][4];
 #pragma unroll
-  for (int j = 0; j < NB; ++j) {
-    acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    if constexpr (GLU) { acu[j][0] = acu[j][1] = acu[j][2] = acu[j][3] = 0.f; }
-  }
-  const int wrow = ROWS >= 64 ? warp * 16 : 0;        // the warp's first row of the tile
-  const int wcol = ROWS >= 64 ? 0 : warp * 16;        // and first column
+  for (int m = 0; m < MB; ++m)
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+      acc[m][j][0] = acc[m][j][1] = acc[m][j][2] = acc[m][j][3] = 0.f;
+      if constexpr (GLU) { acu[m][j][0] = acu[m][j][1] = acu[m][j][2] = acu[m][j][3] = 0.f; }
+    }
+  const int wrow = ROWS >= 64 ? (warp >> 1) * 32 : 0;     // the warp's first row of the tile
+  const int wcol = ROWS >= 64 ? (warp & 1) * 32 : warp * 16;   // and first column
   for (int t = 0; t < ksl; ++t) {
     cp_async_wait<STAGES - 2>();
     __syncthreads();
@@ -124,20 +128,28 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
     const uint32_t st = s0 + (t % STAGES) * STAGE;
 #pragma unroll
     for (int ks = 0; ks < BK / 16; ++ks) {
-      uint32_t af[4];
-      ldmatrix_x4(af, st + (wrow + (lane & 15)) * SROW * 2 + (ks * 2 + (lane >> 4)) * 16);
+      uint32_t af[MB][4];
+#pragma unroll
+      for (int m = 0; m < MB; ++m)
+        ldmatrix_x4(af[m], st + (wrow + m * 16 + (lane & 15)) * SROW * 2 + (ks * 2 + (lane >> 4)) * 16);
 #pragma unroll
       for (int jb = 0; jb < NB / 2; ++jb) {
         uint32_t wf[4];
         const int mi = lane >> 3;
         const uint32_t off = (wcol + jb * 16 + (mi >> 1) * 8 + (lane & 7)) * SROW * 2 + (ks * 2 + (mi & 1)) * 16;
         ldmatrix_x4(wf, st + A_BYTES + off);
-        mma_bf16(acc[2 * jb], af, wf[0], wf[1]);
-        mma_bf16(acc[2 * jb + 1], af, wf[2], wf[3]);
+#pragma unroll
+        for (int m = 0; m < MB; ++m) {
+          mma_bf16(acc[m][2 * jb], af[m], wf[0], wf[1]);
+          mma_bf16(acc[m][2 * jb + 1], af[m], wf[2], wf[3]);
+        }
         if constexpr (GLU) {
           ldmatrix_x4(wf, st + A_BYTES + W_BYTES + off);
-          mma_bf16(acu[2 * jb], af, wf[0], wf[1]);
-          mma_bf16(acu[2 * jb + 1], af, wf[2], wf[3]);
+#pragma unroll
+          for (int m = 0; m < MB; ++m) {
+            mma_bf16(acu[m][2 * jb], af[m], wf[0], wf[1]);
+            mma_bf16(acu[m][2 * jb + 1], af[m], wf[2], wf[3]);
+          }
         }
       }
     }
@@ -145,17 +157,18 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
   cp_async_wait<0>();
   TC* C = (TC*)p.C + (p.tiles ? 0 : (long long)group * p.c_group);
 #pragma unroll
-  for (int hh = 0; hh < 2; ++hh) {
-    const int cr = crow_s[wrow + (lane >> 2) + 8 * hh];
+  for (int mh = 0; mh < 2 * MB; ++mh) {
+    const int m = mh >> 1, hh = mh & 1;
+    const int cr = crow_s[wrow + m * 16 + (lane >> 2) + 8 * hh];
     if (cr < 0) continue;
 #pragma unroll
     for (int j = 0; j < NB; ++j) {
       const int n = n0 + wcol + 8 * j + 2 * (lane & 3);
       if (n >= N) continue;
-      float v0 = acc[j][2 * hh], v1 = acc[j][2 * hh + 1];
+      float v0 = acc[m][j][2 * hh], v1 = acc[m][j][2 * hh + 1];
       if constexpr (GLU) {
         const float g0 = fminf(v0, p.limit), g1 = fminf(v1, p.limit);
-        const float u0 = fminf(fmaxf(acu[j][2 * hh], -p.limit), p.limit), u1 = fminf(fmaxf(acu[j][2 * hh + 1], -p.limit), p.limit);
+        const float u0 = fminf(fmaxf(acu[m][j][2 * hh], -p.limit), p.limit), u1 = fminf(fmaxf(acu[m][j][2 * hh + 1], -p.limit), p.limit);
         v0 = g0 * (1.0f / (1.0f + expf(-p.alpha * g0))) * (u0 + 1.0f);
         v1 = g1 * (1.0f / (1.0f + expf(-p.alpha * g1))) * (u1 + 1.0f);
       }
