@@ -26,16 +26,25 @@ from .allocator import OutOfPages, PageAllocator
 
 @dataclass(frozen=True)
 class KVNeed:
-    """What a mixer needs of the paged cache. window 0: all earlier keys; W: the last W keys (positions p-W+1 .. p)."""
+    """What a mixer needs of the paged cache. window 0: all earlier keys; W: the last W keys (positions p-W+1 .. p).
+    keep_first (with a window): the first tokens of the sequence stay visible too, so the pages that hold them are
+    never given back. value_dim 0: values have the keys' size and the pool is `(slots, pages, 2, kv heads, page_size,
+    head_dim)`; otherwise a token's key and value lie side by side, pool `(slots, pages, kv heads, page_size, head_dim +
+    value_dim)`, and the views of keys and values are strided."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
-
+    value_dim: int = 0
+    keep_first: int = 0
 
     def pool_shape(self, slots: int, pages: int, page_size: int) -> tuple[int, ...]:
+        if self.value_dim:
+            return (slots, pages, self.num_kv_heads, page_size, self.head_dim + self.value_dim)
         return (slots, pages, 2, self.num_kv_heads, page_size, self.head_dim)
 
     def views(self, slot_pool: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor | None]:
+        if self.value_dim:
+            return slot_pool[..., :self.head_dim], slot_pool[..., self.head_dim:]
         return slot_pool[:, 0], slot_pool[:, 1]
 
 
@@ -106,7 +115,8 @@ class KVGroup:
         if not self.need.window or req not in self.rows:
             return
         row, lo = self.rows[req], min(self.first_live_page(computed), self.lens[req])
-        head = row[:lo]
+        kept = -(-getattr(self.need, "keep_first", 0) // self.page_size)      # pages that hold tokens kept for good
+        head = row[kept:lo]
         gone = head[head >= 0]
         if gone.size:
             self.allocator.free(gone.tolist())
@@ -291,6 +301,8 @@ class CacheManager:
             seen: set[int] = set()
             for req, t in g.tables.items():
                 assert all(p >= 0 for p in t[g.first_live_page(self.computed.get(req, 0)):]), f"{req!r} lacks a live page"
+                kept = min(len(t), -(-getattr(g.need, "keep_first", 0) // g.page_size))
+                assert all(p >= 0 for p in t[:kept]), f"{req!r} lost a page of its kept first tokens"
                 for p in t:
                     if p >= 0:
                         assert p not in seen, f"page {p} is in two block tables"

@@ -42,6 +42,15 @@ def _pepilix(c: dict):
 register_architecture("Pepilix", _pepilix)
 
 
+def _gizulorn(c: dict):
+    from .gizulorn import GizulornConfig
+    cfg = GizulornConfig.from_json(c)
+    return cfg, cfg.spec()
+
+
+register_architecture("Gizulorn", _gizulorn)
+
+
 def read_config_json(model_dir: str) -> dict:
     path = os.path.join(model_dir, "config.json")
     if not os.path.isfile(path):

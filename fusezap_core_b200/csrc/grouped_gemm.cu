@@ -21,7 +21,7 @@ struct GroupedArgs {
   int M, N, K;
   const int* tiles;                                     // experts mode: (group, first, count) per row tile; else null
   const int* a_idx; const int* c_idx;                   // experts mode: row maps (null: identity)
-  float alpha, limit;
+  float alpha, limit, up_shift;                         // GLU: g sigmoid(alpha g) (u + up_shift), g and u clamped by limit
   const int* pad_rows; int pad_n, pad_top;              // experts mode, scatter: rows n with pad_rows[n] < 0 have no
                                                         // pairs; their pad_top output rows are written as zeros
 };
@@ -123,7 +123,7 @@ grouped_gemm_kernel(const GroupedArgs p) {
       if constexpr (GLU) {
         const float g = fminf(v, p.limit);
         const float u = fminf(fmaxf(acu[i][j], -p.limit), p.limit);
-        v = g * (1.0f / (1.0f + expf(-p.alpha * g))) * (u + 1.0f);
+        v = g * (1.0f / (1.0f + expf(-p.alpha * g))) * (u + p.up_shift);
       }
       C[(long long)cr * p.ldc + n] = Cvt<TC>::from_f(v);
     }
@@ -150,7 +150,7 @@ route_by_table_kernel(const int* __restrict__ token_ids, const int* __restrict__
   for (int a = threadIdx.x; a < A; a += blockDim.x) {
     const int n = a / top;
     if (seq_row[n] < 0) continue;
-    const int tok = token_ids[n];
+    const int tok = token_ids != nullptr ? token_ids[n] : n;      // no ids: row n of the table belongs to row n
     if (tok < 0 || tok >= V) { atomicOr(err, FZ_ERR_TOKEN_RANGE); continue; }
     const int e = table[(size_t)tok * top + (a - n * top)];
     if (e < 0 || e >= E) { atomicOr(err, FZ_ERR_TOKEN_RANGE); continue; }
@@ -174,7 +174,7 @@ route_by_table_kernel(const int* __restrict__ token_ids, const int* __restrict__
   for (int a = threadIdx.x; a < A; a += blockDim.x) {
     const int n = a / top;
     if (seq_row[n] < 0) continue;
-    const int tok = token_ids[n];
+    const int tok = token_ids != nullptr ? token_ids[n] : n;
     if (tok < 0 || tok >= V) continue;
     const int e = table[(size_t)tok * top + (a - n * top)];
     if (e < 0 || e >= E) continue;
@@ -207,7 +207,7 @@ FZ_API int fz_linear_heads(const void* A, long long lda, long long a_head, const
   if (M <= 0 || N <= 0 || H <= 0) return FZ_OK;
   if (K <= 0) return FZ_BAD_SHAPE;
   if (H > 65535 || (M + BM - 1) / BM > 65535) return FZ_TOO_LARGE;
-  GroupedArgs p = {A, lda, a_head, W, (long long)N * K, C, ldc, c_head, M, N, K, nullptr, nullptr, nullptr, 0.f, 0.f, nullptr, 0, 0};
+  GroupedArgs p = {A, lda, a_head, W, (long long)N * K, C, ldc, c_head, M, N, K, nullptr, nullptr, nullptr, 0.f, 0.f, 0.f, nullptr, 0, 0};
   return dispatch(p, dim3((N + BN - 1) / BN, (M + BM - 1) / BM, H), in_dtype, out_dtype, false, stream);
 }
 
@@ -226,11 +226,11 @@ FZ_API int fz_route_by_table(const int* token_ids, const int* seq_row, const int
 // (pairs, K) in sorted order, C rows through c_idx; pad_rows (may be null): see GroupedArgs.
 FZ_API int fz_grouped_linear(const void* A, const void* W, void* C, const int* tiles, int max_tiles, int tile_rows, const int* a_idx,
                              const int* c_idx, int in_dtype, int out_dtype, int N, int K, int glu, float alpha,
-                             float limit, const int* pad_rows, int pad_n, int pad_top, cudaStream_t stream) {
+                             float limit, float up_shift, const int* pad_rows, int pad_n, int pad_top, cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0) return FZ_OK;
   if (K <= 0 || tile_rows > BM) return FZ_BAD_SHAPE;      // a tile list built for larger row tiles than this kernel's
   if (max_tiles > 65535) return FZ_TOO_LARGE;
-  GroupedArgs p = {A, K, 0, W, (long long)(glu ? 2 : 1) * N * K, C, N, 0, 0, N, K, tiles, a_idx, c_idx, alpha, limit, pad_rows, pad_n, pad_top};
+  GroupedArgs p = {A, K, 0, W, (long long)(glu ? 2 : 1) * N * K, C, N, 0, 0, N, K, tiles, a_idx, c_idx, alpha, limit, up_shift, pad_rows, pad_n, pad_top};
   return dispatch(p, dim3((N + BN - 1) / BN, max_tiles, 1), in_dtype, out_dtype, glu != 0, stream);
 }
 

@@ -35,7 +35,7 @@ struct GroupedArgs {
   void* C; long long ldc; long long c_group;
   int M, N, K;
   const int* tiles; const int* a_idx; const int* c_idx;
-  float alpha, limit;
+  float alpha, limit, up_shift;
   const int* pad_rows; int pad_n, pad_top;
 };
 
@@ -169,8 +169,8 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
       if constexpr (GLU) {
         const float g0 = fminf(v0, p.limit), g1 = fminf(v1, p.limit);
         const float u0 = fminf(fmaxf(acu[m][j][2 * hh], -p.limit), p.limit), u1 = fminf(fmaxf(acu[m][j][2 * hh + 1], -p.limit), p.limit);
-        v0 = g0 * (1.0f / (1.0f + expf(-p.alpha * g0))) * (u0 + 1.0f);
-        v1 = g1 * (1.0f / (1.0f + expf(-p.alpha * g1))) * (u1 + 1.0f);
+        v0 = g0 * (1.0f / (1.0f + expf(-p.alpha * g0))) * (u0 + p.up_shift);
+        v1 = g1 * (1.0f / (1.0f + expf(-p.alpha * g1))) * (u1 + p.up_shift);
       }
       store2<TC>(C + (long long)cr * p.ldc + n, v0, v1);
     }
@@ -219,7 +219,7 @@ FZ_API int fz_linear_heads_tc(const void* A, long long lda, long long a_head, co
   const int rows = M <= 16 ? 16 : M >= 256 ? 128 : 64;
   if (H > 65535 || (M + rows - 1) / rows > 65535) return FZ_TOO_LARGE;
   GroupedArgs p = {(const __nv_bfloat16*)A, lda, a_head, (const __nv_bfloat16*)W, (long long)N * K, C, ldc, c_head, M, N, K,
-                   nullptr, nullptr, nullptr, 0.f, 0.f, nullptr, 0, 0};
+                   nullptr, nullptr, nullptr, 0.f, 0.f, 0.f, nullptr, 0, 0};
   const dim3 grid((N + BN - 1) / BN, (M + rows - 1) / rows, H);
   return rows == 16 ? dispatch<16>(p, grid, out_dtype, false, stream)
        : rows == 64 ? dispatch<64>(p, grid, out_dtype, false, stream) : dispatch<128>(p, grid, out_dtype, false, stream);
@@ -228,12 +228,12 @@ FZ_API int fz_linear_heads_tc(const void* A, long long lda, long long a_head, co
 // Experts mode (see fz_grouped_linear). tile_rows: the rows per tile the tile list was built for: 16, 64 or 128.
 FZ_API int fz_grouped_linear_tc(const void* A, const void* W, void* C, const int* tiles, int max_tiles, int tile_rows,
                                 const int* a_idx, const int* c_idx, int out_dtype, int N, int K, int glu, float alpha,
-                                float limit, const int* pad_rows, int pad_n, int pad_top, cudaStream_t stream) {
+                                float limit, float up_shift, const int* pad_rows, int pad_n, int pad_top, cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0) return FZ_OK;
   if (fz_grouped_tc_check(A, K, 0, W, C, N, 0, N, K) != FZ_OK || (tile_rows != 16 && tile_rows != 64 && tile_rows != 128)) return FZ_BAD_SHAPE;
   if (max_tiles > 65535) return FZ_TOO_LARGE;
   GroupedArgs p = {(const __nv_bfloat16*)A, K, 0, (const __nv_bfloat16*)W, (long long)(glu ? 2 : 1) * N * K, C, N, 0, 0, N, K,
-                   tiles, a_idx, c_idx, alpha, limit, pad_rows, pad_n, pad_top};
+                   tiles, a_idx, c_idx, alpha, limit, up_shift, pad_rows, pad_n, pad_top};
   const dim3 grid((N + BN - 1) / BN, max_tiles, 1);
   return tile_rows == 16 ? dispatch<16>(p, grid, out_dtype, glu != 0, stream)
        : tile_rows == 64 ? dispatch<64>(p, grid, out_dtype, glu != 0, stream) : dispatch<128>(p, grid, out_dtype, glu != 0, stream);

@@ -179,7 +179,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 short_conv_kernel(const T* __restrict__ h, const T* __restrict__ w, const float* __restrict__ state,
                   const int* __restrict__ seg, const int* __restrict__ seq_row, T* __restrict__ out, int C, int taps,
-                  int residual) {
+                  int residual, int act) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   const int n = blockIdx.x;
@@ -204,6 +204,7 @@ short_conv_kernel(const T* __restrict__ h, const T* __restrict__ w, const float*
       acc = fmaf(Cvt<T>::to_f(w[(size_t)c * taps + j]), v, acc);
     }
     if (residual) acc += Cvt<T>::to_f(h[(size_t)n * C + c]);
+    if (act) acc = acc * (1.0f / (1.0f + expf(-acc)));      // silu of the 32-bit sum
     orow[c] = Cvt<T>::from_f(acc);
   }
 }
@@ -237,7 +238,7 @@ template <typename T, int TAPS>
 __global__ void __launch_bounds__(128)
 short_conv_vec_kernel(const T* __restrict__ h, const T* __restrict__ w, const float* __restrict__ state,
                       const int* __restrict__ seg, const int* __restrict__ seq_row, T* __restrict__ out, int C, int taps,
-                      int residual) {
+                      int residual, int act) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   const int n = blockIdx.x;
@@ -279,6 +280,10 @@ short_conv_vec_kernel(const T* __restrict__ h, const T* __restrict__ w, const fl
       ld8(h + (size_t)n * C + c0, v);
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[e] += v[e];
+    }
+    if (act) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = acc[e] * (1.0f / (1.0f + expf(-acc[e])));      // silu of the 32-bit sum
     }
   }
   st8(out + (size_t)n * C + c0, acc);
@@ -436,9 +441,9 @@ rotate_heads_kernel(const T* __restrict__ q, int W, int off, const float* __rest
 }
 template <typename T>
 void launch_conv_vec(dim3 grid, cudaStream_t stream, const T* h, const T* w, const float* state, const int* seg,
-                     const int* seq_row, T* out, int C, int taps, int residual) {
+                     const int* seq_row, T* out, int C, int taps, int residual, int act) {
   const bool w_ok = ((uintptr_t)w & 15) == 0;       // the grouped weight loads want 16-byte aligned rows of 8 x taps values
-#define FZ_CV(N) fz_launch(short_conv_vec_kernel<T, N>, grid, dim3(128), 0, stream, h, w, state, seg, seq_row, out, C, taps, residual)
+#define FZ_CV(N) fz_launch(short_conv_vec_kernel<T, N>, grid, dim3(128), 0, stream, h, w, state, seg, seq_row, out, C, taps, residual, act)
   if (w_ok && taps == 2) FZ_CV(2);
   else if (w_ok && taps == 3) FZ_CV(3);
   else if (w_ok && taps == 4) FZ_CV(4);
@@ -473,20 +478,20 @@ FZ_API int fz_add_rmsnorm_groups(float* x, const float* delta, const void* w, in
 }
 
 FZ_API int fz_short_conv(const void* h, const void* w, float* state, const int* seg, const int* seq_row, void* out,
-                         int dtype, int N, int n_seg, int C, int taps, int residual, cudaStream_t stream) {
+                         int dtype, int N, int n_seg, int C, int taps, int residual, int act, cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
   if (taps < 1 || taps > MAX_TAPS) return FZ_BAD_SHAPE;
   const bool vec = C % 8 == 0 && (((uintptr_t)h | (uintptr_t)out | (uintptr_t)state) & 15) == 0;
   const dim3 vgrid(N, (C / 8 + 127) / 128);
   if (dtype == FZ_F32) {
-    if (vec) launch_conv_vec<float>(vgrid, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual);
-    else fz_launch(short_conv_kernel<float>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual);
+    if (vec) launch_conv_vec<float>(vgrid, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual, act);
+    else fz_launch(short_conv_kernel<float>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual, act);
     FZ_LAUNCH_CHECK();
     if (taps > 1 && state != nullptr && n_seg > 0)
       fz_launch(short_conv_state_kernel<float>, dim3(n_seg, (C + 255) / 256), dim3(256), 0, stream, (const float*)h, state, seg, C, taps);
   } else if (dtype == FZ_BF16) {
-    if (vec) launch_conv_vec<__nv_bfloat16>(vgrid, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual);
-    else fz_launch(short_conv_kernel<__nv_bfloat16>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual);
+    if (vec) launch_conv_vec<__nv_bfloat16>(vgrid, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual, act);
+    else fz_launch(short_conv_kernel<__nv_bfloat16>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual, act);
     FZ_LAUNCH_CHECK();
     if (taps > 1 && state != nullptr && n_seg > 0)
       fz_launch(short_conv_state_kernel<__nv_bfloat16>, dim3(n_seg, (C + 255) / 256), dim3(256), 0, stream, (const __nv_bfloat16*)h, state, seg, C, taps);

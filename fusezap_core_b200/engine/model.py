@@ -214,6 +214,8 @@ def random_model(config: dict, dtype: str = "bfloat16", device: str | torch.devi
     for name, p in model.expected_tensors().items():
         if p.ignore or (p.group is not None and p.group not in groups):
             continue
+        if any(n < 0 for n in p.shape):
+            p = replace(p, shape=p.filled_shape())
         if p.role == "int_table":
             if p.high:      # every row holds distinct values below `high`
                 order = torch.rand((p.shape[0], p.high), generator=gen, device=device).argsort(1)

@@ -23,9 +23,13 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 NVCC_FLAGS += os.environ.get("FZB200_NVCC_EXTRA", "").split()      # extra compiler flags (instrumented builds)
 LIBRARIES: dict[str, list[str]] = {
     "fzb200_core": ["rowwise.cu", "gemm_simt.cu", "attn_simt.cu"],
-    # the gated parallel block, attention over a shared latent cache, products per head and per expert (both dtypes)
-    "fzb200_mix": ["mix_rows.cu", "grouped_gemm.cu", "attn_latent.cu"],
-    "fzb200_mix_tc": ["attn_latent_tc.cu", "grouped_gemm_tc.cu"],                           # bfloat16 only: the same on tensor cores
+    # rows of the gated parallel block and short convolutions, products per head and per expert (both dtypes)
+    "fzb200_mix": ["mix_rows.cu", "grouped_gemm.cu"],
+    "fzb200_mix_tc": ["grouped_gemm_tc.cu"],                                 # bfloat16 only: those products on tensor cores
+    "fzb200_latent": ["attn_latent.cu"],                                     # attention over a shared latent cache (both dtypes)
+    "fzb200_latent_tc": ["attn_latent_tc.cu"],                               # bfloat16 only: the same on tensor cores
+    # recurrent mixers, attention with a window, kept first tokens and a sink, the routed experts' router (both dtypes)
+    "fzb200_seq": ["seq_mix.cu"],
     "fzb200_tc": ["gemm_tc.cu"],                                             # bfloat16 only: tcgen05 / TMA products
     # bfloat16 only: attention over separate keys and values per kv head (tcgen05 / TMA / mma.sync); built when a model
     # with such a mixer asks for it

@@ -55,13 +55,14 @@ class Ops:
         raise NotImplementedError
 
     def short_conv(self, h: torch.Tensor, w: torch.Tensor, state: torch.Tensor | None, meta: Any, out: torch.Tensor,
-                   residual: bool = True) -> None:
+                   residual: bool = True, activation: str | None = None) -> None:
         """Causal convolution over time within each portion of the step (meta.seg: first row, rows, first position,
         state slot). h, out: (N, C) T; w: (C, taps) T; state: (slots, taps - 1, C) float32, the last taps - 1 inputs of
         each request so far, oldest first. For the row at place i of its portion:
         out = (h if residual) + sum_j w[:, j] * in(i - taps + 1 + j), in(k) = h[first row + k] for k >= 0, else
         state[slot, taps - 1 + k]. The sum is float32, j rising, rounded once. Afterwards state[slot] holds the portion's
-        request's last taps - 1 inputs. Padding rows give zeros."""
+        request's last taps - 1 inputs. Padding rows give zeros. activation "silu": out = z * sigmoid(z) of
+        the float32 sum z (residual included), rounded once."""
         raise NotImplementedError
 
     def gated_sum(self, a: torch.Tensor, gate_a: torch.Tensor | None, f: torch.Tensor | None, gate_f: torch.Tensor | None,
@@ -113,15 +114,91 @@ class Ops:
         raise NotImplementedError
 
     def grouped_linear_glu(self, h: torch.Tensor, w: torch.Tensor, route: Any, y: torch.Tensor, alpha: float,
-                           limit: float) -> None:
+                           limit: float, up_shift: float = 1.0) -> None:
         """w: (E, 2 I, K): expert e's gate rows, then its up rows. For every pair (row n, expert e) of the route:
         g = min(w[e, :I] . h[n], limit), u = clamp(w[e, I:] . h[n], -limit, limit), y[pair] = T(g * sigmoid(alpha * g) *
-        (u + 1)); y: (N * top, I) T in the route's own order of pairs; products and activation in float32."""
+        (u + up_shift)); y: (N * top, I) T in the route's own order of pairs; products and activation in float32.
+        (alpha 1, an infinite limit and up_shift 0 give silu(g) * u.)"""
         raise NotImplementedError
 
     def grouped_linear_scatter(self, y: torch.Tensor, w: torch.Tensor, route: Any, out: torch.Tensor) -> None:
         """w: (E, D, I). out[n * top + k] = w[e] . y[pair], float32 (N * top, D), for the pair of row n's k-th choice;
         rows of padding are zero."""
+        raise NotImplementedError
+
+    # ---- recurrent mixers, windowed attention with a sink, routed experts
+    def recurrent_state_shape(self, heads: int, key_dim: int, value_dim: int) -> tuple:
+        """The shape of one request's float32 state for `retention_scan` / `gated_delta_scan`: `heads` matrices of
+        key_dim x value_dim in whatever layout and padding this table's kernels keep them (only they read it; a zeroed
+        slot is the zero state)."""
+        raise NotImplementedError
+
+    def retention_scan(self, proj: torch.Tensor, heads: int, key_dim: int, value_dim: int, decay: torch.Tensor,
+                       key_scale: float, cos: torch.Tensor | None, sin: torch.Tensor | None, rotated: int, pairing: int,
+                       state: torch.Tensor, meta: Any, out: torch.Tensor) -> None:
+        """proj: (N, >= H (2 dk + dv)) float32, a row = [q heads | k heads | v heads | ...]. For every portion of the step
+        (meta.seg), token by token in order, per head h from the state of the portion's slot:
+        S = decay[h] * S + k' v^T, out[n, h] = S^T q' with q' = rot(q), k' = rot(k) * key_scale, where rot turns the
+        first `rotated` dimensions by the row's position (tables (max_len, rotated/2); pairing 0: i with i + rotated/2,
+        1: 2i with 2i+1). out: (N, H dv) float32; everything float32. The slot's state is that after the portion's last
+        token. Padding rows give zeros."""
+        raise NotImplementedError
+
+    def gated_delta_scan(self, qkv: torch.Tensor, heads: int, key_heads: int, key_dim: int, value_dim: int,
+                         high: torch.Tensor, beta: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                         unit_eps: float, query_scale: float, state: torch.Tensor, meta: Any, out: torch.Tensor) -> None:
+        """qkv: (N, 2 Hk dk + H dv) T = [q | k | v]; high: (N, >= H dk) float32 whose first H dk columns are the decay
+        inputs a; beta: (N, H) float32 (before the sigmoid); a_log (H,), dt_bias (H dk,) float32. Per portion, token by
+        token, per head h (key head h // (H / Hk)): q^ = q / sqrt(sum q^2 + unit_eps) * query_scale, k^ likewise without
+        the scale, b = sigmoid(beta), g = exp(-exp(a_log[h]) * softplus(a[h] + dt_bias[h])) per key channel;
+        S = g * S (rows), u = b * (v - S^T k^), S = S + k^ u^T, out[n, h] = S^T q^. float32 throughout; out (N, H dv)."""
+        raise NotImplementedError
+
+    def head_norm_gate(self, o: torch.Tensor, heads: int, value_dim: int, weight: torch.Tensor | None, eps: float,
+                       gate: torch.Tensor | None, gate_offset: int, activation: str | None, out: torch.Tensor) -> None:
+        """o: (N, H dv) float32. out[n, h, c] = T(o / sqrt(mean_c(o[n, h]^2) + eps) * weight[c] * act(gate[n, gate_offset +
+        h dv + c])); weight (dv,) float32 or None (1); gate float32 (N, any width) or None (1); act "silu", "sigmoid"."""
+        raise NotImplementedError
+
+    def check_sink_attention(self, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int) -> None:
+        """Raise ValueError if `sink_attention` cannot take these sizes."""
+        raise NotImplementedError
+
+    def rotate_kv_write(self, qkv: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor | None, rotated: int,
+                        pairing: int, meta: Any, cache: Any, q_out: torch.Tensor, num_heads: int, num_kv_heads: int,
+                        key_dim: int, value_dim: int) -> None:
+        """qkv: (N, Hq dk + Hkv dk + Hkv dv) float32 = [q | k | v]. The first `rotated` dimensions of every q and k head
+        are turned by the row's position (pairing as in `retention_scan`), the rest pass; q goes to q_out (N, Hq dk) T,
+        k and v, rounded once, to the row's place in its request's pages (cache.keys (pages, Hkv, page, dk),
+        cache.values (pages, Hkv, page, dv), any strides with a unit last one)."""
+        raise NotImplementedError
+
+    def sink_attention(self, q: torch.Tensor, cache: Any, meta: Any, out: torch.Tensor, num_heads: int, num_kv_heads: int,
+                       key_dim: int, value_dim: int, scale: float, window: int, keep_first: int,
+                       sink: torch.Tensor | None) -> None:
+        """out[n, h] = sum_j e_j v_j / (sum_j e_j + exp(sink[h] - m)), e_j = exp((q[n, h] . k_j) * scale - m), over the
+        keys j <= p of the row's own request with p - j < window or j < keep_first (window 0: all), p = meta.pos[n], m
+        the largest of the scores and sink[h]; sink None: no such term. kv head h // (Hq / Hkv). out: (N, Hq dv) T."""
+        raise NotImplementedError
+
+    def weighted_sum(self, terms: list, weights: list, out: torch.Tensor) -> None:
+        """out = sum_i weights[i] * terms[i], float32 (N, D), each product rounded, added in the order given."""
+        raise NotImplementedError
+
+    def route_by_scores(self, logits: torch.Tensor, num_experts: int, top: int, groups: int, keep_groups: int,
+                        renormalize: bool, meta: Any, weights: torch.Tensor, align: int = 1) -> Any:
+        """logits: (N, >= E) float32, the first E columns are router logits. s = softmax over them; the experts form
+        `groups` equal groups of neighbours, a group's score is its largest s, only experts of the keep_groups best groups
+        (lower index first among equals) can be chosen; of those the `top` with the largest s (lower index first among
+        equals), in falling order. weights[n, k] = s of the k-th choice (divided by their sum if renormalize); float32.
+        Returns the route of the (row, choice) pairs sorted by expert, as `route_by_table` does."""
+        raise NotImplementedError
+
+    def moe_combine(self, terms: torch.Tensor, weights: torch.Tensor, shared: torch.Tensor | None,
+                    gate_logits: torch.Tensor | None, gate_column: int, out: torch.Tensor) -> None:
+        """out[n] = sum_k weights[n, k] * terms[n * top + k] (+ sigmoid(gate_logits[n, gate_column]) * shared[n]); all
+        float32; terms (N top, D), weights (N, top), shared (N, D), the sum in rising k and the shared term last.
+        Padding rows give zeros."""
         raise NotImplementedError
 
     def linear(self, a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> None:

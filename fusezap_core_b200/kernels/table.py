@@ -120,7 +120,7 @@ class CudaOps(Ops):
         if self.dtype == torch.bfloat16:
             self.tc = load("fzb200_tc")      # tcgen05 / TMA kernels
         self.use_tensor_cores = self.tc is not None
-        self._attn_tc = self._mix = self._mix_tc = None   # libraries loaded (and built) when a part first asks for their kernels
+        self._attn_tc = self._mix = self._mix_tc = self._latent = self._latent_tc = self._seq = None   # libraries loaded (and built) when a part first asks for their kernels
         self.prefill_tcgen05 = True        # False: long portions on the mma.sync flash-attention kernel
         self.fuse_swiglu = True            # gate/up product and SwiGLU in one kernel where the sizes allow it
         self.fuse_argmax = True            # lm_head product and argmax in one pass where no logits are asked for
@@ -133,6 +133,7 @@ class CudaOps(Ops):
         self.latent_tensor_cores = True    # latent attention on tensor cores where the sizes allow it (bfloat16)
         self.cut_prefill_keys = True       # few query tiles with many keys behind them are cut along the keys
         self._profile = None               # a StepProfile while the engine profiles its steps
+        self._meta_rows = None             # meta.seq_row of the step being run, for ops that take no `meta`
         # the fewest query heads, and the fewest items of a query tile on the prompt kernel, among the attention layers
         # that `check_attention` has seen (the plan of a step is shared by its layers)
         self._attn_heads = self._attn_items = 0
@@ -141,7 +142,7 @@ class CudaOps(Ops):
     # ---- plumbing
     @property
     def mix_tc(self):
-        """The tensor-core attention over a shared latent cache (bfloat16)."""
+        """The products per head and per expert on tensor cores (bfloat16)."""
         if self._mix_tc is None:
             self._mix_tc = load("fzb200_mix_tc")
         return self._mix_tc
@@ -152,6 +153,27 @@ class CudaOps(Ops):
         if self._attn_tc is None:
             self._attn_tc = load("fzb200_attn_tc")
         return self._attn_tc
+
+    @property
+    def latent(self):
+        """The general attention over a shared latent cache."""
+        if self._latent is None:
+            self._latent = load("fzb200_latent")
+        return self._latent
+
+    @property
+    def latent_tc(self):
+        """The tensor-core attention over a shared latent cache (bfloat16)."""
+        if self._latent_tc is None:
+            self._latent_tc = load("fzb200_latent_tc")
+        return self._latent_tc
+
+    @property
+    def seq(self):
+        """The recurrent scans, the attention with a window, kept first tokens and a sink, the experts' router."""
+        if self._seq is None:
+            self._seq = load("fzb200_seq")
+        return self._seq
 
     @property
     def mix(self):
@@ -580,7 +602,9 @@ class CudaOps(Ops):
             raise KernelError("select_tokens: row counts differ")
         self._check(self.mix.fz_select_tokens(_p(tokens), _p(src), _p(prev_ids), _p(out), c_int(n), self._stream()), "select_tokens")
 
-    def short_conv(self, h, w, state, meta, out, residual: bool = True) -> None:
+    def short_conv(self, h, w, state, meta, out, residual: bool = True, activation: str | None = None) -> None:
+        if activation not in (None, "silu"):
+            raise KernelError(f"short_conv: activation {activation!r} is not one of None, 'silu'")
         self._want(h, "convolution input", (self.dtype,), 2)
         self._want(w, "convolution weight", (self.dtype,), 2)
         self._want(out, "convolution output", (self.dtype,), 2)
@@ -595,8 +619,8 @@ class CudaOps(Ops):
             if tuple(state.shape[1:]) != (taps - 1, c):
                 raise KernelError(f"short_conv: state {tuple(state.shape)}, expected (slots, {taps - 1}, {c})")
         self._check(self.mix.fz_short_conv(_p(h), _p(w), _p(state), _p(meta.seg), _p(meta.seq_row), _p(out),
-                                           c_int(_CODE[self.dtype]), c_int(n), c_int(meta.n_segments), c_int(c), c_int(taps),
-                                           c_int(1 if residual else 0), self._stream()), "short_conv",
+                                           c_int(_CODE[self.dtype]), c_int(n), c_int(meta.max_segments), c_int(c), c_int(taps),
+                                           c_int(1 if residual else 0), c_int(1 if activation else 0), self._stream()), "short_conv",
                     n * c * 2 * h.element_size())
         if taps > 1:
             self.launches += 1    # the state update
@@ -618,11 +642,11 @@ class CudaOps(Ops):
 
     # ---- latent attention
     def check_latent_attention(self, num_heads: int, key_width: int, value_width: int) -> None:
-        if self.mix.fz_attn_latent_check(c_int(num_heads), c_int(key_width), c_int(value_width)) != 0:
+        if self.latent.fz_attn_latent_check(c_int(num_heads), c_int(key_width), c_int(value_width)) != 0:
             raise ValueError(f"latent attention sizes not supported: {num_heads} heads, cached vectors of {key_width} "
                              f"values of which {value_width} are read as values (need value <= key <= 1024, value <= 512)")
         if self.use_tensor_cores and self.latent_tensor_cores:
-            self.mix_tc       # built and loaded with the model, not at its first step
+            self.latent_tc    # built and loaded with the model, not at its first step
 
     def _latent_pool(self, cache, width: int):
         pool = cache.keys
@@ -702,18 +726,18 @@ class CudaOps(Ops):
         if self._profile is not None:
             nbytes = contexts(list(getattr(meta, "segments", ()))) * width * pool.element_size() + n * heads * (width + value_width) * q.element_size()
         if self.use_tensor_cores and self.latent_tensor_cores and \
-                self.mix_tc.fz_attn_latent_tc_check(c_int(heads), c_int(width), c_int(value_width)) == 0:
+                self.latent_tc.fz_attn_latent_tc_check(c_int(heads), c_int(width), c_int(value_width)) == 0:
             blocks = n * heads // 64 + max(1, int(getattr(meta, "latent_extra", 0)) or n)
             # few tiles with many keys behind them (decoded tokens): the keys are cut into ranges, merged by a second kernel
             ctx = max(1, int(meta.max_context))
-            splits = int(self.mix_tc.fz_attn_latent_tc_splits(c_int(blocks), c_int(ctx), c_int(self._sms))) if self.latent_key_cuts else 1
+            splits = int(self.latent_tc.fz_attn_latent_tc_splits(c_int(blocks), c_int(ctx), c_int(self._sms))) if self.latent_key_cuts else 1
             scratch = None
             if splits > 1:
-                self.mix_tc.fz_attn_latent_tc_scratch.restype = c_longlong
+                self.latent_tc.fz_attn_latent_tc_scratch.restype = c_longlong
                 scratch = self._scratch("latent attention partials",
-                                        int(self.mix_tc.fz_attn_latent_tc_scratch(c_int(blocks), c_int(splits), c_int(value_width))),
+                                        int(self.latent_tc.fz_attn_latent_tc_scratch(c_int(blocks), c_int(splits), c_int(value_width))),
                                         torch.float32)
-            self._check(self.mix_tc.fz_attn_latent_tc(
+            self._check(self.latent_tc.fz_attn_latent_tc(
                 _p(q), _p(pool), _p(meta.seq_row), _p(meta.seg), c_int(meta.n_segments), _p(table), c_int(table.shape[1]),
                 c_longlong(page_stride), c_int(cache.page_size), c_int(pool.shape[0]), _p(out), c_int(n), c_int(blocks),
                 c_int(heads), c_int(width), c_int(value_width), c_float(scale), c_int(window), c_int(splits), c_int(ctx),
@@ -721,7 +745,7 @@ class CudaOps(Ops):
                 "latent_attention (tensor cores)", nbytes)
             self.launches += 2 if splits > 1 else 1    # the kernel that zeroes rows of padding, the merge kernel
             return
-        self._check(self.mix.fz_attn_latent(
+        self._check(self.latent.fz_attn_latent(
             _p(q), _p(pool), _p(meta.pos), _p(meta.seq_row), _p(table), c_int(table.shape[1]), c_longlong(page_stride),
             c_int(cache.page_size), c_int(pool.shape[0]), _p(out), c_int(_CODE[self.dtype]), c_int(n), c_int(heads),
             c_int(width), c_int(value_width), c_float(scale), c_int(window), _p(self.err), self._stream()),
@@ -731,7 +755,11 @@ class CudaOps(Ops):
     def route_by_table(self, token_ids, meta, table, num_experts, align: int = 1):
         self._want(token_ids, "token ids", (torch.int32,), 1)
         self._want(table, "expert table", (torch.int32,), 2)
-        n, top = token_ids.shape[0], table.shape[1]
+        return self._sort_pairs(token_ids, token_ids.shape[0], meta, table, num_experts, align)
+
+    def _sort_pairs(self, token_ids, n, meta, table, num_experts, align):
+        """The step's (row, choice) pairs sorted by expert table[id of the row, choice] (no ids: table[row, choice])."""
+        top = table.shape[1]
         # row tiles of 64 pairs; of 16 where an expert gets few rows (decoded tokens) and the tensor-core kernels run
         tile = int(self.mix.fz_grouped_tile_rows())
         if self.use_tensor_cores and self.grouped_tensor_cores and n * top <= 16 * num_experts:
@@ -752,7 +780,7 @@ class CudaOps(Ops):
                     self.mix_tc.fz_grouped_tc_check(_p(a), c_longlong(lda), c_longlong(0), _p(w), _p(c), c_longlong(ldc),
                                                     c_longlong(0), c_int(n_out), c_int(k)) == 0)
 
-    def grouped_linear_glu(self, h, w, route, y, alpha, limit) -> None:
+    def grouped_linear_glu(self, h, w, route, y, alpha, limit, up_shift: float = 1.0) -> None:
         a_idx, c_idx, tiles, max_tiles, n, top, seq_row, tile = route
         self._want(h, "expert input", (self.dtype,), 2)
         self._want(w, "expert gate/up weights", (self.dtype,), 3)
@@ -764,12 +792,12 @@ class CudaOps(Ops):
         if self._grouped_tc(h, k, w, y, inter, inter, k):
             self._check(self.mix_tc.fz_grouped_linear_tc(_p(h), _p(w), _p(y), _p(tiles), c_int(max_tiles), c_int(tile), _p(a_idx),
                                                          c_void_p(0), c_int(_CODE[y.dtype]), c_int(inter), c_int(k), c_int(1),
-                                                         c_float(alpha), c_float(limit), c_void_p(0), c_int(0), c_int(0),
+                                                         c_float(alpha), c_float(limit), c_float(up_shift), c_void_p(0), c_int(0), c_int(0),
                                                          self._stream()), "grouped_linear_glu (tensor cores)", nbytes)
             return
         self._check(self.mix.fz_grouped_linear(_p(h), _p(w), _p(y), _p(tiles), c_int(max_tiles), c_int(tile), _p(a_idx), c_void_p(0),
                                                c_int(_CODE[self.dtype]), c_int(_CODE[self.dtype]), c_int(inter), c_int(k),
-                                               c_int(1), c_float(alpha), c_float(limit), c_void_p(0), c_int(0), c_int(0),
+                                               c_int(1), c_float(alpha), c_float(limit), c_float(up_shift), c_void_p(0), c_int(0), c_int(0),
                                                self._stream()),
                     "grouped_linear_glu", (min(w.shape[0], n * top) * 2 * inter * k + n * k + n * top * inter) * h.element_size())
 
@@ -785,11 +813,207 @@ class CudaOps(Ops):
         if self._grouped_tc(y, inter, w, out, d, d, inter):
             self._check(self.mix_tc.fz_grouped_linear_tc(_p(y), _p(w), _p(out), _p(tiles), c_int(max_tiles), c_int(tile),
                                                          c_void_p(0), _p(c_idx), c_int(_CODE[out.dtype]), c_int(d), c_int(inter),
-                                                         c_int(0), c_float(0.0), c_float(0.0), _p(seq_row), c_int(n), c_int(top),
+                                                         c_int(0), c_float(0.0), c_float(0.0), c_float(0.0), _p(seq_row), c_int(n), c_int(top),
                                                          self._stream()), "grouped_linear_scatter (tensor cores)", nbytes)
             return
         self._check(self.mix.fz_grouped_linear(_p(y), _p(w), _p(out), _p(tiles), c_int(max_tiles), c_int(tile), c_void_p(0), _p(c_idx),
                                                c_int(_CODE[self.dtype]), c_int(_CODE[torch.float32]), c_int(d), c_int(inter),
-                                               c_int(0), c_float(0.0), c_float(0.0), _p(seq_row), c_int(n), c_int(top),
+                                               c_int(0), c_float(0.0), c_float(0.0), c_float(0.0), _p(seq_row), c_int(n), c_int(top),
                                                self._stream()),
                     "grouped_linear_scatter", min(w.shape[0], n * top) * d * inter * y.element_size() + n * top * (inter * y.element_size() + d * 4))
+
+    # ---- recurrent mixers, attention with a window, kept first tokens and a sink, routed experts
+    def recurrent_state_shape(self, heads: int, key_dim: int, value_dim: int) -> tuple:
+        """(heads, value_dim, padded key_dim): a column of S is contiguous, padded to 16 times a power of two."""
+        pad = int(self.seq.fz_recurrent_key_pad(c_int(key_dim)))
+        if pad < 0:
+            raise ValueError(f"a recurrent state with {key_dim} key dimensions is not supported (1..512)")
+        return (heads, value_dim, pad)
+
+    def _state(self, state, heads, key_dim, value_dim, what):
+        self._want(state, f"{what} state", (torch.float32,), 4)
+        if tuple(state.shape[1:]) != self.recurrent_state_shape(heads, key_dim, value_dim):
+            raise KernelError(f"{what}: state {tuple(state.shape)}, expected (slots, "
+                              f"{', '.join(map(str, self.recurrent_state_shape(heads, key_dim, value_dim)))})")
+
+    def _tables(self, cos, sin, rotated, what):
+        if not rotated:
+            return 0
+        self._want(cos, "cos table", (torch.float32,), 2)
+        self._want(sin, "sin table", (torch.float32,), 2)
+        if rotated % 2 or cos.shape[1] != rotated // 2 or sin.shape != cos.shape:
+            raise KernelError(f"{what}: {rotated} rotated dimensions, cos {tuple(cos.shape)}, sin {tuple(sin.shape)}")
+        return cos.shape[0]
+
+    def retention_scan(self, proj, heads, key_dim, value_dim, decay, key_scale, cos, sin, rotated, pairing, state, meta, out) -> None:
+        self._want(proj, "retention projections", (torch.float32,), 2)
+        self._want(decay, "decay", (torch.float32,), 1)
+        self._want(out, "retention output", (torch.float32,), 2)
+        n, ld = proj.shape
+        if ld < heads * (2 * key_dim + value_dim) or tuple(out.shape) != (n, heads * value_dim) or decay.shape[0] != heads:
+            raise KernelError(f"retention_scan: proj {tuple(proj.shape)}, out {tuple(out.shape)}, decay {tuple(decay.shape)}")
+        self._state(state, heads, key_dim, value_dim, "retention_scan")
+        self._meta_rows = meta.seq_row
+        max_pos = self._tables(cos, sin, rotated, "retention_scan")
+        self._check(self.seq.fz_retention_scan(
+            _p(proj), c_int(ld), c_int(heads), c_int(key_dim), c_int(value_dim), _p(decay), c_float(key_scale),
+            _p(cos if rotated else None), _p(sin if rotated else None), c_int(rotated), c_int(pairing), c_int(max_pos), _p(state),
+            _p(meta.seg), c_int(meta.max_segments), _p(out), _p(self.err), self._stream()), "retention_scan",
+            n * heads * (2 * key_dim + 2 * value_dim) * 4 + 2 * meta.n_segments * heads * value_dim * state.shape[3] * 4)
+
+    def gated_delta_scan(self, qkv, heads, key_heads, key_dim, value_dim, high, beta, a_log, dt_bias, unit_eps, query_scale,
+                         state, meta, out) -> None:
+        self._want(qkv, "q/k/v", (self.dtype,), 2)
+        self._want(high, "decay inputs", (torch.float32,), 2)
+        self._want(beta, "beta", (torch.float32,), 2)
+        self._want(a_log, "decay rates", (torch.float32,), 1)
+        self._want(dt_bias, "decay bias", (torch.float32,), 1)
+        self._want(out, "delta-rule output", (torch.float32,), 2)
+        n = qkv.shape[0]
+        if qkv.shape[1] != 2 * key_heads * key_dim + heads * value_dim or high.shape[0] != n or high.shape[1] < heads * key_dim \
+                or tuple(beta.shape) != (n, heads) or a_log.shape[0] != heads or dt_bias.shape[0] != heads * key_dim \
+                or tuple(out.shape) != (n, heads * value_dim) or heads % key_heads:
+            raise KernelError(f"gated_delta_scan: qkv {tuple(qkv.shape)}, high {tuple(high.shape)}, beta {tuple(beta.shape)}, "
+                              f"out {tuple(out.shape)}")
+        self._state(state, heads, key_dim, value_dim, "gated_delta_scan")
+        self._meta_rows = meta.seq_row
+        self._check(self.seq.fz_gated_delta_scan(
+            _p(qkv), c_int(_CODE[self.dtype]), c_int(heads), c_int(key_heads), c_int(key_dim), c_int(value_dim), _p(high),
+            c_int(high.shape[1]), _p(beta), _p(a_log), _p(dt_bias), c_float(unit_eps), c_float(query_scale), _p(state),
+            _p(meta.seg), c_int(meta.max_segments), _p(out), self._stream()), "gated_delta_scan",
+            n * (qkv.shape[1] * qkv.element_size() + heads * (key_dim + value_dim + 1) * 4)
+            + 2 * meta.n_segments * heads * value_dim * state.shape[3] * 4)
+
+    def head_norm_gate(self, o, heads, value_dim, weight, eps, gate, gate_offset, activation, out) -> None:
+        self._want(o, "head outputs", (torch.float32,), 2)
+        self._want(out, "normed head outputs", (torch.float32, self.dtype), 2)
+        n = o.shape[0]
+        if o.shape[1] != heads * value_dim or out.shape != o.shape:
+            raise KernelError(f"head_norm_gate: o {tuple(o.shape)}, out {tuple(out.shape)}, {heads} heads of {value_dim}")
+        if weight is not None:
+            self._want(weight, "head norm weight", (torch.float32,), 1)
+            if weight.shape[0] != value_dim:
+                raise KernelError(f"head_norm_gate: weight {tuple(weight.shape)} for heads of {value_dim}")
+        act = {None: 0, "sigmoid": 1, "silu": 2}.get(activation, -1)
+        if act < 0:
+            raise KernelError(f"head_norm_gate: activation {activation!r} is not one of None, 'sigmoid', 'silu'")
+        ldg = 0
+        if gate is not None:
+            self._want(gate, "gate", (torch.float32,), 2)
+            ldg = gate.shape[1]
+            if gate.shape[0] != n or gate_offset + heads * value_dim > ldg or act == 0:
+                raise KernelError(f"head_norm_gate: gate {tuple(gate.shape)} from column {gate_offset}, activation {activation!r}")
+        seq_row = self._step_rows(n)
+        self._check(self.seq.fz_head_norm_gate(_p(o), c_int(n), c_int(heads), c_int(value_dim), _p(weight), c_float(eps),
+                                               _p(gate), c_int(ldg), c_int(gate_offset), c_int(act if gate is not None else 0),
+                                               _p(seq_row), _p(out), c_int(_CODE[out.dtype]), self._stream()),
+                    "head_norm_gate", n * heads * value_dim * (4 + (4 if gate is not None else 0) + out.element_size()))
+
+    def _step_rows(self, n: int):
+        """meta.seq_row of the step being run (the ops that take no `meta` still zero their rows of padding)."""
+        rows = self._meta_rows
+        if rows is None or rows.shape[0] != n:
+            raise KernelError("the step's rows are not known: `route_by_scores`, `rotate_kv_write` or a scan must run first")
+        return rows
+
+    def check_sink_attention(self, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int) -> None:
+        if self.seq.fz_sink_attention_check(c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim)) != 0:
+            raise ValueError(f"attention sizes not supported: {num_heads} heads, {num_kv_heads} kv heads, key size {key_dim}, "
+                             f"value size {value_dim} (need heads % kv_heads == 0 and sizes of 1..512)")
+
+    def _kv_views(self, cache, hkv: int, dk: int, dv: int):
+        k, v = cache.keys, cache.values
+        for t, name, d in ((k, "key pool", dk), (v, "value pool", dv)):
+            if not t.is_cuda or t.dtype != self.dtype:
+                raise KernelError(f"{name}: device {t.device}, dtype {t.dtype}; expected CUDA {self.dtype}")
+            if t.dim() != 4 or t.shape[1] != hkv or t.shape[2] != cache.page_size or t.shape[3] != d or t.stride(3) != 1:
+                raise KernelError(f"{name} has shape {tuple(t.shape)} and strides {t.stride()}, expected (pages, {hkv}, "
+                                  f"{cache.page_size}, {d}) with a unit last stride")
+        if k.stride()[:3] != v.stride()[:3]:
+            raise KernelError("key and value pools have different strides")
+        return k, v
+
+    def rotate_kv_write(self, qkv, cos, sin, rotated, pairing, meta, cache, q_out, num_heads, num_kv_heads, key_dim, value_dim) -> None:
+        self._want(qkv, "qkv", (torch.float32,), 2)
+        self._want(q_out, "q", (self.dtype,), 2)
+        n = qkv.shape[0]
+        if qkv.shape[1] != (num_heads + num_kv_heads) * key_dim + num_kv_heads * value_dim or tuple(q_out.shape) != (n, num_heads * key_dim):
+            raise KernelError(f"rotate_kv_write: qkv {tuple(qkv.shape)}, q {tuple(q_out.shape)}")
+        max_pos = self._tables(cos, sin, rotated, "rotate_kv_write")
+        k, v = self._kv_views(cache, num_kv_heads, key_dim, value_dim)
+        table = meta.table(cache.group)
+        self._check(self.seq.fz_rotate_kv_write(
+            _p(qkv), _p(cos if rotated else None), _p(sin if rotated else None), c_int(rotated), c_int(pairing), c_int(max_pos),
+            _p(meta.pos), _p(meta.seq_row), _p(table), c_int(table.shape[1]), _p(k), _p(v), c_longlong(k.stride(0)),
+            c_longlong(k.stride(1)), c_longlong(k.stride(2)), c_int(cache.page_size), c_int(k.shape[0]),
+            c_int(1 if cache.write else 0), _p(q_out), c_int(_CODE[self.dtype]), c_int(n), c_int(num_heads), c_int(num_kv_heads),
+            c_int(key_dim), c_int(value_dim), _p(self.err), self._stream()), "rotate_kv_write",
+            n * qkv.shape[1] * (4 + q_out.element_size()))
+
+    def sink_attention(self, q, cache, meta, out, num_heads, num_kv_heads, key_dim, value_dim, scale, window, keep_first, sink) -> None:
+        self._want(q, "q", (self.dtype,), 2)
+        self._want(out, "attention output", (self.dtype,), 2)
+        n = q.shape[0]
+        if q.shape[1] != num_heads * key_dim or tuple(out.shape) != (n, num_heads * value_dim):
+            raise KernelError(f"sink_attention: q {tuple(q.shape)}, out {tuple(out.shape)}")
+        if sink is not None:
+            self._want(sink, "sinks", (torch.float32,), 1)
+            if sink.shape[0] != num_heads:
+                raise KernelError(f"sink_attention: {tuple(sink.shape)} sinks for {num_heads} heads")
+        k, v = self._kv_views(cache, num_kv_heads, key_dim, value_dim)
+        table = meta.table(cache.group)
+        nbytes = 0
+        if self._profile is not None:
+            seen = sum(min(sg.pos0 + i + 1, (window + keep_first) if window else sg.pos0 + i + 1) for sg in meta.segments for i in range(sg.n))
+            nbytes = seen * num_kv_heads * (key_dim + value_dim) * k.element_size() + n * num_heads * (key_dim + value_dim) * q.element_size()
+        self._check(self.seq.fz_sink_attention(
+            _p(q), _p(k), _p(v), _p(meta.pos), _p(meta.seq_row), _p(table), c_int(table.shape[1]), c_longlong(k.stride(0)),
+            c_longlong(k.stride(1)), c_longlong(k.stride(2)), c_int(cache.page_size), c_int(k.shape[0]), _p(out),
+            c_int(_CODE[self.dtype]), c_int(n), c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim),
+            c_float(scale), c_int(window), c_int(keep_first), _p(sink), _p(self.err), self._stream()), "sink_attention", nbytes)
+
+    def weighted_sum(self, terms, weights, out) -> None:
+        if not 1 <= len(terms) <= 4 or len(weights) != len(terms):
+            raise KernelError(f"weighted_sum: {len(terms)} terms and {len(weights)} weights (1 to 4 of each)")
+        self._want(out, "sum", (torch.float32,), 2)
+        for t in terms:
+            self._want(t, "term", (torch.float32,), 2)
+            if t.shape != out.shape:
+                raise KernelError(f"weighted_sum: term {tuple(t.shape)}, out {tuple(out.shape)}")
+        ts = list(terms) + [None] * (4 - len(terms))
+        ws = [float(w) for w in weights] + [0.0] * (4 - len(weights))
+        self._check(self.seq.fz_weighted_sum(*(_p(t) for t in ts), *(c_float(w) for w in ws), c_int(len(terms)), _p(out),
+                                             c_longlong(out.numel()), self._stream()), "weighted_sum",
+                    out.numel() * 4 * (len(terms) + 1))
+
+    def route_by_scores(self, logits, num_experts, top, groups, keep_groups, renormalize, meta, weights, align: int = 1):
+        self._want(logits, "router logits", (torch.float32,), 2)
+        self._want(weights, "router weights", (torch.float32,), 2)
+        n = logits.shape[0]
+        if logits.shape[1] < num_experts or tuple(weights.shape) != (n, top):
+            raise KernelError(f"route_by_scores: logits {tuple(logits.shape)}, weights {tuple(weights.shape)}, {num_experts} experts")
+        choice = self._scratch("router choices", max(n, 1) * top, torch.int32)[:n * top].view(n, top)
+        self._check(self.seq.fz_router_topk(_p(logits), c_int(logits.shape[1]), c_int(n), c_int(num_experts), c_int(top),
+                                            c_int(groups), c_int(keep_groups), c_int(1 if renormalize else 0), _p(meta.seq_row),
+                                            _p(choice), _p(weights), self._stream()), "router_topk")
+        self._meta_rows = meta.seq_row
+        return self._sort_pairs(None, n, meta, choice, num_experts, align)
+
+    def moe_combine(self, terms, weights, shared, gate_logits, gate_column, out) -> None:
+        self._want(terms, "expert terms", (torch.float32,), 2)
+        self._want(weights, "router weights", (torch.float32,), 2)
+        self._want(out, "feed-forward output", (torch.float32,), 2)
+        n, top = weights.shape
+        d = out.shape[1]
+        if tuple(terms.shape) != (n * top, d) or out.shape[0] != n:
+            raise KernelError(f"moe_combine: terms {tuple(terms.shape)}, weights {tuple(weights.shape)}, out {tuple(out.shape)}")
+        ldg = 0
+        if shared is not None:
+            self._want(shared, "shared expert output", (torch.float32,), 2)
+            self._want(gate_logits, "shared gate logits", (torch.float32,), 2)
+            ldg = gate_logits.shape[1]
+            if shared.shape != out.shape or gate_logits.shape[0] != n or not 0 <= gate_column < ldg:
+                raise KernelError(f"moe_combine: shared {tuple(shared.shape)}, gate logits {tuple(gate_logits.shape)} column {gate_column}")
+        self._check(self.seq.fz_moe_combine(_p(terms), _p(weights), c_int(top), _p(shared), _p(gate_logits), c_int(ldg),
+                                            c_int(gate_column), _p(self._step_rows(n)), _p(out), c_int(n), c_int(d), self._stream()),
+                    "moe_combine", n * d * 4 * (top + 1 + (shared is not None)))

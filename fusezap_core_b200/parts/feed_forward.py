@@ -15,15 +15,17 @@ from .base import FeedForward, register_feed_forward
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
     def __init__(self, hidden_size: int, intermediate_size: int,
-                 names: tuple[str, str, str] = ("gate_proj", "up_proj", "down_proj")):
-        self.D, self.I, self.names = hidden_size, intermediate_size, tuple(names)
+                 names: tuple[str, str, str] = ("gate_proj", "up_proj", "down_proj"), suffix: str = ".weight"):
+        """suffix: what follows a matrix's name in the checkpoint ("" where the name alone is the tensor)."""
+        self.D, self.I, self.names, self.suffix = hidden_size, intermediate_size, tuple(names), suffix
         self.wgu = self.bgu = self.wd = self.bd = self.packed = None
 
     def tensors(self) -> dict[str, ParamSpec]:
         g, u, d = self.names
+        sx = self.suffix
         return {
-            f"{g}.weight": ParamSpec((self.I, self.D)), f"{u}.weight": ParamSpec((self.I, self.D)),
-            f"{d}.weight": ParamSpec((self.D, self.I)),
+            f"{g}{sx}": ParamSpec((self.I, self.D)), f"{u}{sx}": ParamSpec((self.I, self.D)),
+            f"{d}{sx}": ParamSpec((self.D, self.I)),
             f"{g}.bias": ParamSpec((self.I,), role="vector", group="gate_up_bias"),
             f"{u}.bias": ParamSpec((self.I,), role="vector", group="gate_up_bias"),
             f"{d}.bias": ParamSpec((self.D,), role="vector", group="down_bias"),
@@ -31,25 +33,27 @@ class SwiGLU(FeedForward):
 
     def bind(self, tensors, ops) -> None:
         g, u, d = self.names
+        sx = self.suffix
         # the kernel table may want gate and up in a layout of its own for a fused product + activation
-        self.packed = ops.pack_gate_up(tensors[f"{g}.weight"], tensors[f"{u}.weight"], tensors.get(f"{g}.bias"),
+        self.packed = ops.pack_gate_up(tensors[f"{g}{sx}"], tensors[f"{u}{sx}"], tensors.get(f"{g}.bias"),
                                        tensors.get(f"{u}.bias"))
         if self.packed is None:
-            self.wgu = torch.cat([tensors[f"{g}.weight"], tensors[f"{u}.weight"]], 0).contiguous()
+            self.wgu = torch.cat([tensors[f"{g}{sx}"], tensors[f"{u}{sx}"]], 0).contiguous()
             if f"{g}.bias" in tensors:
                 self.bgu = torch.cat([tensors[f"{g}.bias"].float(), tensors[f"{u}.bias"].float()], 0).contiguous()
-        self.wd = tensors[f"{d}.weight"]
+        self.wd = tensors[f"{d}{sx}"]
         self.bd = tensors[f"{d}.bias"].float() if f"{d}.bias" in tensors else None
 
-    def forward(self, ctx, h: torch.Tensor) -> torch.Tensor:
+    def forward(self, ctx, h: torch.Tensor, tag: str = "") -> torch.Tensor:
+        """tag: a prefix for the names of its scratch buffers (a feed-forward that runs inside another one)."""
         n, ops, ws = h.shape[0], ctx.ops, ctx.ws
-        a = ws.get("act", (n, self.I), ops.dtype)
+        a = ws.get(tag + "act", (n, self.I), ops.dtype)
         if self.packed is not None:
             ops.linear_swiglu(h, self.packed, a)
         else:
-            gu = ws.get("gate_up", (n, 2 * self.I), ops.dtype)
+            gu = ws.get(tag + "gate_up", (n, 2 * self.I), ops.dtype)
             ops.linear(h, self.wgu, self.bgu, gu)
             ops.swiglu(gu, a)
-        delta = ws.get("delta", (n, self.D), torch.float32)
+        delta = ws.get(tag + "delta", (n, self.D), torch.float32)
         ops.linear(a, self.wd, self.bd, delta)
         return delta

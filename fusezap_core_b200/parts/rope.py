@@ -42,13 +42,23 @@ class RotaryEncoding(PositionEncoding):
                  low_freq_factor: float = 1.0, high_freq_factor: float = 4.0,
                  original_max_position_embeddings: int = 0, precise: bool = False):
         """precise: frequencies theta^(-2j/head_dim) and angles p * f_j are computed in 64-bit and the cosines and sines
-        rounded once to float32 (default: in float32 throughout, as the dense decoder's reference does)."""
+        rounded once to float32 (default: in float32 throughout, as the dense decoder's reference does). The tables
+        serve any pairing of dimensions: a mixer that rotates in its own kernels (neighbouring dimensions paired, only
+        the first dimensions of a head rotated) reads `cos` / `sin` (max_len, head_dim / 2) by pair index."""
         if head_dim % 2:
             raise ValueError(f"rope needs an even head_dim, got {head_dim}")
         self.head_dim, self.precise = head_dim, bool(precise)
-        if precise and kind != "default":
-            raise NotImplementedError("precise angles are computed for unscaled frequencies only")
+        if precise and kind not in ("default", "llama3"):
+            raise NotImplementedError("precise angles are computed for unscaled and for llama3-scaled frequencies only")
         self.inv_freq64 = np.float64(theta) ** (-np.arange(0, head_dim, 2, dtype=np.float64) / np.float64(head_dim))
+        if precise and kind == "llama3":
+            # by wavelength l = 2 pi / f: short ones (l < old / high) stay, long ones (l > old / low) are divided by
+            # `factor`, those between are blended with s = (old / l - low) / (high - low); all in 64-bit
+            f, old = self.inv_freq64, float(original_max_position_embeddings)
+            wl = 2 * math.pi / f
+            s = (old / wl - low_freq_factor) / (high_freq_factor - low_freq_factor)
+            self.inv_freq64 = np.where(wl < old / high_freq_factor, f,
+                                       np.where(wl > old / low_freq_factor, f / factor, (1 - s) * f / factor + s * f))
         self.inv_freq = inverse_frequencies(head_dim, theta, kind, factor, low_freq_factor, high_freq_factor,
                                             original_max_position_embeddings)
         self.cos: torch.Tensor | None = None

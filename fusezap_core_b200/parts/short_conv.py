@@ -14,8 +14,12 @@ from .base import Part
 
 
 class ShortConv(Part):
-    def __init__(self, size: int, taps: int, name: str = "weight", residual: bool = True):
-        """residual: the result is `h + conv(h)` (what a block hands on in place of h); False: `conv(h)` alone."""
+    def __init__(self, size: int, taps: int, name: str = "weight", residual: bool = True, activation: str | None = None):
+        """residual: the result is `h + conv(h)` (what a block hands on in place of h); False: `conv(h)` alone.
+        activation: None, or "silu" (`z * sigmoid(z)` of the 32-bit sum, before the one rounding)."""
+        if activation not in (None, "silu"):
+            raise ValueError(f"activation {activation!r} is not one of None, 'silu'")
+        self.activation = activation
         if taps < 1:
             raise ValueError(f"a convolution needs at least one tap, got {taps}")
         self.size, self.taps, self.name, self.residual = size, int(taps), name, bool(residual)
@@ -34,5 +38,8 @@ class ShortConv(Part):
         """h: (N, size) T; state: (slots, taps - 1, size) float32 (None when taps == 1). Returns (N, size) T and leaves
         the state of every portion's request at the portion's end."""
         out = ctx.ws.get(tag, tuple(h.shape), h.dtype)
-        ctx.ops.short_conv(h, self.weight, state, ctx.meta, out, self.residual)
+        if self.activation is None:
+            ctx.ops.short_conv(h, self.weight, state, ctx.meta, out, self.residual)
+        else:
+            ctx.ops.short_conv(h, self.weight, state, ctx.meta, out, self.residual, self.activation)
         return out

@@ -45,7 +45,7 @@ def check_tensors(expected: dict[str, ParamSpec], found: dict[str, torch.Tensor]
         p = expected.get(name)
         if p is None or p.ignore:
             continue
-        if tuple(t.shape) != tuple(p.shape):
+        if len(t.shape) != len(p.shape) or any(want >= 0 and have != want for have, want in zip(t.shape, p.shape)):
             wrong.append(f"{name}: shape {tuple(t.shape)}, expected {tuple(p.shape)}")
         elif p.role == "int_table" and t.dtype in _FLOATS:
             wrong.append(f"{name}: dtype {t.dtype}, expected an integer table")

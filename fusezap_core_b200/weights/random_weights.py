@@ -11,6 +11,8 @@ import json
 import os
 from typing import Iterator
 
+from dataclasses import replace
+
 import numpy as np
 import torch
 
@@ -31,6 +33,8 @@ def distinct_rows(rng: np.random.Generator, shape: tuple[int, ...], high: int) -
 
 
 def draw(rng: np.random.Generator, p: ParamSpec, norm_noise: bool, optional: bool) -> torch.Tensor:
+    if any(n < 0 for n in p.shape):
+        p = replace(p, shape=p.filled_shape())
     if p.role == "int_table":
         return torch.from_numpy(distinct_rows(rng, p.shape, p.high))
     if p.init == "ones":

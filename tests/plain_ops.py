@@ -163,7 +163,7 @@ class PlainOpsWide(PlainOps):
     def select_tokens(self, tokens, src, prev_ids, out) -> None:
         out.copy_(torch.where(src >= 0, prev_ids[src.long().clamp(min=0)], tokens))
 
-    def short_conv(self, h, w, state, meta, out, residual=True) -> None:
+    def short_conv(self, h, w, state, meta, out, residual=True, activation=None) -> None:
         taps = w.shape[1]
         out.zero_()
         wf = w.float()
@@ -175,7 +175,10 @@ class PlainOpsWide(PlainOps):
             y = torch.zeros_like(rows)
             for j in range(taps):
                 y = y + wf[:, j] * line[j: j + sg.n]
-            out[sg.row0: sg.row0 + sg.n] = (acc + y).to(out.dtype)
+            z = acc + y
+            if activation == "silu":
+                z = z * torch.sigmoid(z)
+            out[sg.row0: sg.row0 + sg.n] = z.to(out.dtype)
             if taps > 1:
                 state[sg.state_slot] = line[line.shape[0] - (taps - 1):]
 
@@ -245,16 +248,159 @@ class PlainOpsWide(PlainOps):
         assert ((ex >= 0) & (ex < num_experts)).all()
         return ex, meta.seq_row >= 0
 
-    def grouped_linear_glu(self, h, w, route, y, alpha, limit) -> None:
+    def grouped_linear_glu(self, h, w, route, y, alpha, limit, up_shift=1.0) -> None:
         ex, live = route
         I = w.shape[1] // 2
         wf = w.float()[ex]                                           # (N, top, 2I, K)
         gu = torch.einsum("ntik,nk->nti", wf, h.float())
         g, u = gu[..., :I].clamp(max=limit), gu[..., I:].clamp(-limit, limit)
-        act = g * (1.0 / (1.0 + torch.exp(-alpha * g))) * (u + 1)
+        act = g * (1.0 / (1.0 + torch.exp(-alpha * g))) * (u + up_shift)
         y.copy_(torch.where(live[:, None, None], act, torch.zeros(())).reshape(y.shape).to(y.dtype))
 
     def grouped_linear_scatter(self, y, w, route, out) -> None:
         ex, live = route
         t = torch.einsum("ntdi,nti->ntd", w.float()[ex], y.view(ex.shape[0], ex.shape[1], -1).float())
         out.copy_(torch.where(live[:, None, None], t, torch.zeros(())).reshape(out.shape))
+
+
+class PlainOpsSeq(PlainOpsWide):
+    """The operations of the recurrent mixers, the windowed attention with a sink and the routed experts."""
+
+    def recurrent_state_shape(self, heads, key_dim, value_dim):
+        return (heads, key_dim, value_dim)
+
+    def _rot(self, x, cos, sin, rotated, pairing, pos):
+        """x: (N, heads, d) float; the first `rotated` dimensions turned by pos."""
+        if not rotated:
+            return x
+        c, s = cos[pos][:, None, :].to(x.dtype), sin[pos][:, None, :].to(x.dtype)
+        out = x.clone()
+        if pairing == 1:
+            u, v = x[..., 0:rotated:2], x[..., 1:rotated:2]
+            out[..., 0:rotated:2], out[..., 1:rotated:2] = u * c - v * s, v * c + u * s
+        else:
+            half = rotated // 2
+            u, v = x[..., :half], x[..., half:rotated]
+            out[..., :half], out[..., half:rotated] = u * c - v * s, v * c + u * s
+        return out
+
+    def retention_scan(self, proj, heads, key_dim, value_dim, decay, key_scale, cos, sin, rotated, pairing, state, meta, out):
+        H, dk, dv = heads, key_dim, value_dim
+        out.zero_()
+        pos = meta.pos.long()
+        for sg in meta.segments:
+            r = slice(sg.row0, sg.row0 + sg.n)
+            x = proj[r].double()
+            q = self._rot(x[:, :H * dk].reshape(-1, H, dk), cos, sin, rotated, pairing, pos[r])
+            k = self._rot(x[:, H * dk: 2 * H * dk].reshape(-1, H, dk), cos, sin, rotated, pairing, pos[r]) * key_scale
+            v = x[:, 2 * H * dk: 2 * H * dk + H * dv].reshape(-1, H, dv)
+            S = state[sg.state_slot].double()
+            for t in range(sg.n):
+                S = decay.double()[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
+                out[sg.row0 + t] = torch.einsum("hkv,hk->hv", S, q[t]).reshape(-1).float()
+            state[sg.state_slot] = S.float()
+
+    def gated_delta_scan(self, qkv, heads, key_heads, key_dim, value_dim, high, beta, a_log, dt_bias, unit_eps, query_scale,
+                         state, meta, out):
+        H, Hk, dk, dv = heads, key_heads, key_dim, value_dim
+        out.zero_()
+        rep = H // Hk
+        for sg in meta.segments:
+            r = slice(sg.row0, sg.row0 + sg.n)
+            x = qkv[r].double()
+            q = x[:, :Hk * dk].reshape(-1, Hk, dk)
+            k = x[:, Hk * dk: 2 * Hk * dk].reshape(-1, Hk, dk)
+            v = x[:, 2 * Hk * dk:].reshape(-1, H, dv)
+            q = (q / torch.sqrt((q * q).sum(-1, keepdim=True) + unit_eps) * query_scale).repeat_interleave(rep, 1)
+            k = (k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)).repeat_interleave(rep, 1)
+            b = torch.sigmoid(beta[r].double())
+            a = high[r, :H * dk].double() + dt_bias.double()
+            g = torch.exp(-torch.exp(a_log.double())[None, :, None] * torch.nn.functional.softplus(a).reshape(-1, H, dk))
+            S = state[sg.state_slot].double()
+            for t in range(sg.n):
+                S = g[t][:, :, None] * S
+                u = b[t][:, None] * (v[t] - torch.einsum("hkv,hk->hv", S, k[t]))
+                S = S + k[t][:, :, None] * u[:, None, :]
+                out[sg.row0 + t] = torch.einsum("hkv,hk->hv", S, q[t]).reshape(-1).float()
+            state[sg.state_slot] = S.float()
+
+    def head_norm_gate(self, o, heads, value_dim, weight, eps, gate, gate_offset, activation, out):
+        n = o.shape[0]
+        x = o.view(n, heads, value_dim)
+        y = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)
+        if weight is not None:
+            y = y * weight.float()
+        if gate is not None:
+            z = gate[:, gate_offset: gate_offset + heads * value_dim].reshape(n, heads, value_dim)
+            y = y * (torch.sigmoid(z) if activation == "sigmoid" else z * torch.sigmoid(z))
+        out.copy_(y.reshape(n, -1).to(out.dtype))
+
+    def check_sink_attention(self, num_heads, num_kv_heads, key_dim, value_dim) -> None:
+        if num_heads % num_kv_heads:
+            raise ValueError("bad attention sizes")
+
+    def rotate_kv_write(self, qkv, cos, sin, rotated, pairing, meta, cache, q_out, num_heads, num_kv_heads, key_dim, value_dim):
+        n, Hq, Hkv, dk, dv = qkv.shape[0], num_heads, num_kv_heads, key_dim, value_dim
+        pos, row = meta.pos.long(), meta.seq_row.long()
+        q = self._rot(qkv[:, :Hq * dk].reshape(n, Hq, dk), cos, sin, rotated, pairing, pos)
+        k = self._rot(qkv[:, Hq * dk: (Hq + Hkv) * dk].reshape(n, Hkv, dk), cos, sin, rotated, pairing, pos)
+        v = qkv[:, (Hq + Hkv) * dk:].reshape(n, Hkv, dv)
+        live = row >= 0
+        q_out.copy_(torch.where(live[:, None, None], q, torch.zeros(())).reshape(n, -1).to(q_out.dtype))
+        table, bs = meta.table(cache.group), cache.page_size
+        for i in range(n):
+            if not live[i] or not cache.write:
+                continue
+            page = int(table[row[i], pos[i] // bs])
+            assert page >= 0, "a position has no page"
+            cache.keys[page, :, pos[i] % bs] = k[i].to(cache.keys.dtype)
+            cache.values[page, :, pos[i] % bs] = v[i].to(cache.values.dtype)
+
+    def sink_attention(self, q, cache, meta, out, num_heads, num_kv_heads, key_dim, value_dim, scale, window, keep_first, sink):
+        n, Hq, Hkv, dk, dv = q.shape[0], num_heads, num_kv_heads, key_dim, value_dim
+        pos, row = meta.pos.long(), meta.seq_row.long()
+        table, bs = meta.table(cache.group), cache.page_size
+        out.zero_()
+        for i in range(n):
+            if row[i] < 0:
+                continue
+            p = int(pos[i])
+            js = [j for j in range(p + 1) if not window or p - j < window or j < keep_first]
+            pages = [int(table[row[i], j // bs]) for j in js]
+            assert min(pages) >= 0, "a visible key has no page"
+            K = torch.stack([cache.keys[pg, :, j % bs] for pg, j in zip(pages, js)]).float()      # (J, Hkv, dk)
+            V = torch.stack([cache.values[pg, :, j % bs] for pg, j in zip(pages, js)]).float()
+            qi = q[i].float().view(Hkv, Hq // Hkv, dk)
+            s = torch.einsum("gak,jgk->gaj", qi, K) * scale
+            if sink is not None:
+                s = torch.cat([s, sink.float().view(Hkv, Hq // Hkv, 1)], -1)
+            w = torch.softmax(s, -1)[..., :len(js)]
+            out[i] = torch.einsum("gaj,jgv->gav", w, V).reshape(-1).to(out.dtype)
+
+    def weighted_sum(self, terms, weights, out) -> None:
+        acc = torch.zeros_like(out)
+        for t, w in zip(terms, weights):
+            acc = acc + torch.tensor(w, dtype=torch.float32) * t
+        out.copy_(acc)
+
+    def route_by_scores(self, logits, num_experts, top, groups, keep_groups, renormalize, meta, weights, align=1):
+        E = num_experts
+        s = torch.softmax(logits[:, :E].float(), -1)
+        per = E // groups
+        gs = s.view(-1, groups, per).max(-1).values
+        best = torch.sort(gs, dim=-1, descending=True, stable=True).indices[:, :keep_groups]
+        allowed = torch.zeros_like(gs, dtype=torch.bool).scatter_(1, best, True).repeat_interleave(per, 1)
+        masked = torch.where(allowed, s, torch.full_like(s, -1.0))
+        order = torch.sort(masked, dim=-1, descending=True, stable=True).indices[:, :top]
+        w = torch.gather(s, 1, order)
+        if renormalize:
+            w = w / w.sum(-1, keepdim=True)
+        weights.copy_(w)
+        return order, meta.seq_row >= 0
+
+    def moe_combine(self, terms, weights, shared, gate_logits, gate_column, out) -> None:
+        n, top = weights.shape
+        acc = (terms.view(n, top, -1) * weights[:, :, None]).sum(1)
+        if shared is not None:
+            acc = acc + torch.sigmoid(gate_logits[:, gate_column: gate_column + 1]) * shared
+        out.copy_(acc)
