@@ -1,7 +1,7 @@
 """Benchmark: decode tokens per second of the Llama-3.1-8B-sized model (random bf16 weights) on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L] [--impl ours|reference]
-                    [--preset NAME] [--workload decode|stream|pepilix]
+                    [--preset NAME] [--workload decode|stream|pepilix|gizulorn]
 
 A "step" is one decode step of `--batch` requests whose contexts end at `--context` tokens. Prints ONE JSON line:
   value      decoded tokens per second, timed on the device (CUDA events around K steps: metadata copy + graph replay)
@@ -23,6 +23,8 @@ with prompt lengths uniform in [16, 1024] and 256 new tokens each, one arriving 
 `LLMEngine.add_request` / `step()`; the line's value is generated tokens per second of wall clock from the first
 arrival to the last token.
 
+`--workload gizulorn` (`--sizes g1024,g2048`, `--layers 4`) does the same for the Gizulorn design (retention, attention with
+a window and a sink beside the gated delta rule, routed experts with a shared one).
 `--workload pepilix` (`--sizes w1024,w2048`, `--layers 4`) times the Pepilix design beside the dense decoder at equal
 width, layers, heads, vocabulary and active feed-forward size: a 2,048-token prompt and decode steps at `--batch`
 requests through `LLMEngine.step()`, and (unless `--no-points`) a kernel-by-kernel profile of both; its line's `sizes`
@@ -154,7 +156,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--reference-device", default="CUDA", help="the reference's device name for --impl reference")
-    ap.add_argument("--workload", default="decode", choices=["decode", "stream", "pepilix"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "stream", "pepilix", "gizulorn"],
                     help="pepilix: prefill and decode of the Pepilix design at a few layer sizes, beside the dense decoder "
                          "at equal width, layers, heads and active feed-forward size")
     ap.add_argument("--sizes", default="w1024,w2048", help="pepilix workload: which of its sizes to run")
@@ -184,6 +186,8 @@ def main() -> int:
         return stream_workload(a)
     if a.workload == "pepilix":
         return pepilix_workload(a)
+    if a.workload == "gizulorn":
+        return design_workload(a, "gizulorn")
 
     import numpy as np
     import torch
@@ -406,8 +410,41 @@ PEPILIX_SIZES = {
 }
 
 
+# Layer sizes for the Gizulorn workload: (width, heads, key size, value size, kv heads of the attention, window, key heads
+# of the delta rule, experts, top, groups, kept groups, expert ff, shared ff, vocab). Layers alternate retention, parallel
+# (attention beside the delta rule), retention, retention; every layer has routed experts. The dense decoder beside it
+# has the same width, layers, heads and vocabulary, head size 64 or 128 with a quarter as many kv heads, and an
+# intermediate size of top x expert ff + shared ff (the same active weights per token).
+GIZULORN_SIZES = {
+    "g1024": (1024, 8, 64, 128, 2, 512, 4, 16, 2, 4, 2, 512, 512, 32768),
+    "g2048": (2048, 16, 128, 128, 4, 1024, 8, 32, 4, 8, 4, 512, 1024, 32768),
+}
+
+
+def gizulorn_configs(name: str, L: int, ctx: int):
+    D, H, dk, dv, kv, window, kh, E, top, groups, keep, ff, shared, V = GIZULORN_SIZES[name]
+    ret = {"heads": H, "dim": dk, "vdim": dv, "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(1, H - 1)) for h in range(H)],
+           "rot": {"base": 1e6, "dims": dk}}
+    par = {"left": {"heads": H, "kv_heads": kv, "dim": dk, "vdim": dk, "scale": dk ** -0.5, "mask": {"size": window, "keep_first": 4},
+                    "rot": {"base": 5e5, "dims": dk, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+           "left_scale": 0.8, "right": {"heads": H, "kv_heads": kh, "dim": dk, "vdim": dv, "conv": 4}, "right_scale": 0.5}
+    mlp = {"kind": "moe", "router": {"experts": E, "top": top, "groups": {"count": groups, "keep": keep}}, "expert": {"ff": ff},
+           "shared": {"ff": shared}}
+    layers = [{"type": "parallel" if i % 4 == 1 else "retention", "mixer": par if i % 4 == 1 else ret, "mlp": mlp} for i in range(L)]
+    giz = {"architecture": "Gizulorn", "vocab": V, "width": D, "norm": {"eps": 1e-6}, "layers": layers}
+    dense = {"model_type": "llama", "hidden_size": D, "intermediate_size": top * ff + shared, "num_hidden_layers": L,
+             "num_attention_heads": H, "num_key_value_heads": max(1, H // 4), "head_dim": 64 if dk <= 64 else 128,
+             "vocab_size": V, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "max_position_embeddings": ctx,
+             "tie_word_embeddings": True}
+    return giz, dense
+
+
 def pepilix_workload(a) -> int:
-    """`--workload pepilix`: for each size, a 2,048-token prompt (median of five) and decode steps at --batch requests
+    return design_workload(a, "pepilix")
+
+
+def design_workload(a, design: str) -> int:
+    """`--workload pepilix` / `--workload gizulorn`: for each size, a 2,048-token prompt (median of five) and decode steps at --batch requests
     with contexts near --context, through `LLMEngine.step()`, for Pepilix and for the dense decoder at equal size; then
     one profiled prompt and decode step of each (kernel by kernel, CUDA events) for the share and GB/s of every kernel
     class. Random bf16 weights, --layers layers (default 4)."""
@@ -422,7 +459,11 @@ def pepilix_workload(a) -> int:
     pk = peaks()
     rng = np.random.default_rng(5)
 
+    SIZES = PEPILIX_SIZES if design == "pepilix" else GIZULORN_SIZES
+
     def configs(name):
+        if design == "gizulorn":
+            return gizulorn_configs(name, L, ctx)
         D, H, dn, dr, dv, r, E, top, ff, V = PEPILIX_SIZES[name]
         mixer = {"heads": H, "dim": dn, "rot_dim": dr, "vdim": dv, "kv_rank": r, "scale": (dn + dr) ** -0.5,
                  "rot": {"base": 10000.0, "dims": dr}}
@@ -498,14 +539,15 @@ def pepilix_workload(a) -> int:
     clocks = ClockSampler()
     clocks.start()
     sizes, launches = {}, 0
-    for name in [n for n in a.sizes.split(",") if n]:
-        if name not in PEPILIX_SIZES:
-            raise SystemExit(f"--sizes: {name!r} is not one of {sorted(PEPILIX_SIZES)}")
+    chosen = a.sizes if design == "pepilix" or a.sizes != "w1024,w2048" else ",".join(GIZULORN_SIZES)
+    for name in [n for n in chosen.split(",") if n]:
+        if name not in SIZES:
+            raise SystemExit(f"--sizes: {name!r} is not one of {sorted(SIZES)}")
         pep, dense = configs(name)
-        res = {"pepilix": run(pep, False), "dense": run(dense, False)}
-        launches += res["pepilix"].pop("launches", 0) + res["dense"].pop("launches", 0)
+        res = {design: run(pep, False), "dense": run(dense, False)}
+        launches += res[design].pop("launches", 0) + res["dense"].pop("launches", 0)
         if not a.no_points:
-            for which, cfg in (("pepilix", pep), ("dense", dense)):
+            for which, cfg in ((design, pep), ("dense", dense)):
                 prof = run(cfg, True)
                 for k in ("prefill_classes", "decode_classes"):
                     res[which][k] = [{"class": c["class"], "launches": c["launches"], "ms": c["ms"], "share": c["share"],
@@ -515,12 +557,14 @@ def pepilix_workload(a) -> int:
     clk = clocks.stop()
     first = sizes[next(iter(sizes))]
     print(json.dumps({
-        "metric": "pepilix_decode_tokens_per_s", "value": first["pepilix"]["decode"]["tok_s"], "unit": "tok/s", "n_gpus": 1,
-        "steps": a.steps, "warmup": a.warmup, "ms_per_step": first["pepilix"]["decode"]["ms_per_step"], "higher_is_better": True,
+        "metric": f"{design}_decode_tokens_per_s", "value": first[design]["decode"]["tok_s"], "unit": "tok/s", "n_gpus": 1,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": first[design]["decode"]["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"workload": "pepilix", "layers": L, "global_batch": batch, "seq_len": ctx, "page_size": page,
-                   "sizes": {n: dict(zip(("width", "heads", "dim", "rot_dim", "vdim", "kv_rank", "experts", "top", "ff", "vocab"),
-                                         PEPILIX_SIZES[n])) for n in sizes},
+        "config": {"workload": design, "layers": L, "global_batch": batch, "seq_len": ctx, "page_size": page,
+                   "sizes": {n: dict(zip(("width", "heads", "dim", "rot_dim", "vdim", "kv_rank", "experts", "top", "ff", "vocab")
+                                         if design == "pepilix" else
+                                         ("width", "heads", "dim", "vdim", "kv_heads", "window", "key_heads", "experts", "top", "groups",
+                                          "keep", "ff", "shared_ff", "vocab"), SIZES[n])) for n in sizes},
                    "weights": "random N(0,0.02)", "peaks": pk["source"], "l2": "inputs larger than L2"},
         "clocks": clk, "gpu_launches": int(launches), "sizes": sizes}))
     return 0

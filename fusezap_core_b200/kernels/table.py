@@ -619,7 +619,7 @@ class CudaOps(Ops):
             if tuple(state.shape[1:]) != (taps - 1, c):
                 raise KernelError(f"short_conv: state {tuple(state.shape)}, expected (slots, {taps - 1}, {c})")
         self._check(self.mix.fz_short_conv(_p(h), _p(w), _p(state), _p(meta.seg), _p(meta.seq_row), _p(out),
-                                           c_int(_CODE[self.dtype]), c_int(n), c_int(meta.max_segments), c_int(c), c_int(taps),
+                                           c_int(_CODE[self.dtype]), c_int(n), c_int(getattr(meta, "max_segments", meta.n_segments)), c_int(c), c_int(taps),
                                            c_int(1 if residual else 0), c_int(1 if activation else 0), self._stream()), "short_conv",
                     n * c * 2 * h.element_size())
         if taps > 1:

@@ -94,5 +94,5 @@ def tokens_for(cfg: dict, lengths, seed: int) -> list[list[int]]:
 
 
 def rounded(w: dict) -> dict:
-    """The weights as a bfloat16 engine holds them (matrices rounded once)."""
-    return {k: v.to(torch.bfloat16).to(torch.float32) if v.dtype.is_floating_point else v for k, v in w.items()}
+    """The weights as a bfloat16 engine holds them: matrices rounded once, vectors stored in 32-bit as they are."""
+    return {k: v.to(torch.bfloat16).to(torch.float32) if v.dim() >= 2 else v for k, v in w.items()}
