@@ -68,138 +68,307 @@ rotate_kv_write_kernel(const float* __restrict__ qkv, const float* __restrict__ 
 }
 
 // ------------------------------------------------------------------------------ attention: window, kept tokens, sink
-// One block per (token row, kv head, slice of up to 32 query heads of the kv head's group); warp w serves the query heads
-// w, w + W, ... of the slice. Keys are walked in chunks of 32 whose boundaries are multiples of 32 in absolute position,
-// first the chunks of the kept first tokens that lie before the window, then the window's, and the running (max, sum,
-// accumulator) is updated chunk by chunk; the sink enters last. The order of every sum depends only on the row's own
-// position, never on the batch, the cut of the prompt or the pages used.
+// A (row, query head) pair is served by one warp. Keys are walked in chunks of 32 whose boundaries are multiples of 32 in
+// absolute position, first the chunks of the kept first tokens that lie before the window, then the window's; lane j
+// scores key 32c + j and the running (max, sum, accumulator) is updated chunk by chunk; the sink enters last. A chunk in
+// which a pair sees no key leaves its running values exactly as they are, so the order and the bits of every sum depend
+// only on the row's own position, never on the batch, the cut of the prompt, the pages used or which rows share a block.
+//
+// Two kernels with the same arithmetic per chunk: `sink_attention_tile_kernel` gives a block up to 32 pairs of
+// consecutive rows of one portion and one kv head (the rows share every key / value load); `sink_attention_unit_kernel`
+// (steps of single tokens) gives a block a run of a row's chunks and leaves (max, sum, accumulator) per run for
+// `sink_attention_merge_kernel`, which adds the runs up in rising order.
 constexpr int CHUNK = 32;
-constexpr int MAX_WARPS = 8;
-constexpr int MAX_HPW = 4;
-constexpr int MAX_GROUP = MAX_WARPS * MAX_HPW;
+constexpr int ATT_WARPS = 8;
+constexpr int MAX_PPW = 4;                         // pairs per warp
+constexpr int MAX_PAIRS = ATT_WARPS * MAX_PPW;     // pairs per block
 
-template <typename T, int DPL>   // DPL: value dims per lane = ceil(dv / 32)
-__global__ void sink_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
-                                      const int* __restrict__ pos, const int* __restrict__ seq_row,
-                                      const int* __restrict__ table, int mb, long long page_stride, long long head_stride,
-                                      long long tok_stride, int page_size, int n_pages, T* __restrict__ out, int Hq, int Hkv,
-                                      int dk, int dv, float scale, int window, int keep_first,
-                                      const float* __restrict__ sink, int* err) {
-  fz_grid_launch_dependents();
-  fz_grid_wait();
-  extern __shared__ float smem[];
-  const int n = blockIdx.x, kvh = blockIdx.y;
-  const int G_all = Hq / Hkv, g_base = blockIdx.z * MAX_GROUP;
-  const int G = min(MAX_GROUP, G_all - g_base);
+struct AttnArgs {
+  const void* q; const void* k_pool; const void* v_pool;
+  const int* pos; const int* seq_row; const int* seg; const int* table;
+  int mb; long long page_stride, head_stride, tok_stride;
+  int page_size, n_pages;
+  void* out; int Hq, Hkv, dk, dv;
+  float scale; int window, keep_first;
+  const float* sink; int* err;
+  int N;                                           // rows of the step
+  int rows_per_block;                              // tile kernel: rows of a portion per block
+  int unit_chunks, max_units; float* part;         // unit kernel: chunks per run, runs per row, (m, l, acc[dv]) per (row, head, run)
+};
+
+// The chunks a row at position p walks: `first_end + 1` chunks of kept tokens, then chunks c2 .. p / CHUNK.
+struct ChunkWalk {
+  int lo, kept, first_end, c2, count;
+  __device__ ChunkWalk(int p_first, int p_last, int window, int keep_first) {
+    lo = window > 0 ? max(0, p_first - window + 1) : 0;
+    kept = min(keep_first, lo);                    // keys 0 .. kept-1 are seen although they lie before the window
+    first_end = kept > 0 ? (kept - 1) / CHUNK : -1;
+    c2 = max(lo / CHUNK, first_end + 1);
+    count = first_end + 1 + max(0, p_last / CHUNK - c2 + 1);
+  }
+  __device__ int chunk(int it) const { return it <= first_end ? it : c2 + (it - first_end - 1); }
+};
+
+// All threads of the block: keys and values of chunk c of kv head `kvh` that some row of the block may see, as floats.
+template <typename T>
+__device__ __forceinline__ void load_chunk(const AttnArgs& a, const int* trow, int kvh, int c, int lo, int kept, int p_last,
+                                           float* Ks, float* Vs) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, W = blockDim.x >> 5;
-  const int kstride = dk + 1;
-  float* Ks = smem;                       // [CHUNK][dk + 1]
-  float* Vs = Ks + CHUNK * kstride;       // [CHUNK][dv]
-  float* Qs = Vs + CHUNK * dv;            // [G][dk]
-  const int head0 = kvh * G_all + g_base;
-  T* orow = out + ((size_t)n * Hq + head0) * dv;
-  const int row = seq_row[n];
-  if (row < 0) {
-    for (int i = threadIdx.x; i < G * dv; i += blockDim.x) orow[i] = Cvt<T>::from_f(0.f);
-    return;
+  const T* kp = (const T*)a.k_pool;
+  const T* vp = (const T*)a.v_pool;
+  for (int j = warp; j < CHUNK; j += W) {
+    const int key = c * CHUNK + j;
+    long long off = -1;
+    if (key <= p_last && (key >= lo || key < kept)) {
+      const int page = trow[key / a.page_size];
+      if (page < 0 || page >= a.n_pages) { if (lane == 0) atomicOr(a.err, FZ_ERR_NO_PAGE); }
+      else off = (long long)page * a.page_stride + (long long)kvh * a.head_stride + (long long)(key % a.page_size) * a.tok_stride;
+    }
+    for (int d = lane; d < a.dk; d += 32) Ks[j * (a.dk + 1) + d] = off >= 0 ? Cvt<T>::to_f(kp[off + d]) : 0.f;
+    for (int d = lane; d < a.dv; d += 32) Vs[j * a.dv + d] = off >= 0 ? Cvt<T>::to_f(vp[off + d]) : 0.f;
   }
-  const int p = pos[n];
-  const int lo = window > 0 ? max(0, p - window + 1) : 0;
-  const int kept = min(keep_first, lo);                      // keys 0 .. kept-1 are seen although they lie before the window
-  const T* qrow = q + ((size_t)n * Hq + head0) * dk;
-  for (int i = threadIdx.x; i < G * dk; i += blockDim.x) Qs[i] = Cvt<T>::to_f(qrow[i]);
+}
 
-  float m[MAX_HPW], l[MAX_HPW], acc[MAX_HPW][DPL];
+// One warp, one pair, one chunk: the online-softmax update. A chunk without a visible key changes nothing.
+template <int DPL>
+__device__ __forceinline__ void pair_chunk(const float* qh, const float* Ks, const float* Vs, int c, int p, int lo,
+                                           int keep_first, float scale, int dk, int dv, float& m, float& l, float* acc) {
+  const int lane = threadIdx.x & 31;
+  const int key = c * CHUNK + lane;
+  const bool valid = key <= p && (key >= lo || key < keep_first);
+  const float* kr = Ks + lane * (dk + 1);
+  float s = 0.f;
+  for (int d = 0; d < dk; ++d) s = fmaf(qh[d], kr[d], s);
+  s = valid ? s * scale : -INFINITY;
+  const float mn = fmaxf(m, warp_max(s));
+  if (mn == -INFINITY) return;                     // nothing seen so far, nothing here
+  const float pj = valid ? expf(s - mn) : 0.f;
+  const float corr = expf(m - mn);                 // 0 for the pair's first chunk (m = -inf), 1 where nothing is seen
+  l = l * corr + warp_sum(pj);
+  m = mn;
 #pragma unroll
-  for (int a = 0; a < MAX_HPW; ++a) {
-    m[a] = -INFINITY;
-    l[a] = 0.f;
-#pragma unroll
-    for (int i = 0; i < DPL; ++i) acc[a][i] = 0.f;
-  }
-  const int* trow = table + (size_t)row * mb;
-  const long long head_off = (long long)kvh * head_stride;
-  const int first_end = kept > 0 ? (kept - 1) / CHUNK : -1;      // last chunk of the kept tokens
-  const int c2 = max(lo / CHUNK, first_end + 1);                 // first chunk of the window not yet walked
-  const int c_last = p / CHUNK;
-  for (int it = 0;; ++it) {
-    const int c = it <= first_end ? it : c2 + (it - first_end - 1);
-    if (c > c_last) break;
-    __syncthreads();   // the previous chunk is consumed (and Qs is written, the first time)
-    for (int j = warp; j < CHUNK; j += W) {
-      const int key = c * CHUNK + j;
-      const bool seen = key <= p && (key >= lo || key < kept);
-      long long off = -1;
-      if (seen) {
-        const int page = trow[key / page_size];
-        if (page < 0 || page >= n_pages) { if (lane == 0) atomicOr(err, FZ_ERR_NO_PAGE); }
-        else off = (long long)page * page_stride + head_off + (long long)(key % page_size) * tok_stride;
-      }
-      for (int d = lane; d < dk; d += 32) Ks[j * kstride + d] = off >= 0 ? Cvt<T>::to_f(k_pool[off + d]) : 0.f;
-      for (int d = lane; d < dv; d += 32) Vs[j * dv + d] = off >= 0 ? Cvt<T>::to_f(v_pool[off + d]) : 0.f;
-    }
-    __syncthreads();
-    const int key = c * CHUNK + lane;
-    const bool valid = key <= p && (key >= lo || key < kept);
-#pragma unroll
-    for (int a = 0; a < MAX_HPW; ++a) {
-      const int g = warp + a * W;
-      if (g >= G) break;
-      const float* qh = Qs + g * dk;
-      const float* kr = Ks + lane * kstride;
-      float s = 0.f;
-      for (int d = 0; d < dk; ++d) s = fmaf(qh[d], kr[d], s);
-      s = valid ? s * scale : -INFINITY;
-      const float mn = fmaxf(m[a], warp_max(s));       // finite: every chunk walked holds at least one visible key
-      const float pj = valid ? expf(s - mn) : 0.f;
-      const float corr = expf(m[a] - mn);               // 0 for the first chunk (m = -inf)
-      l[a] = l[a] * corr + warp_sum(pj);
-      m[a] = mn;
-#pragma unroll
-      for (int i = 0; i < DPL; ++i) acc[a][i] *= corr;
-      for (int j = 0; j < CHUNK; ++j) {
-        const float pv = __shfl_sync(0xffffffffu, pj, j);
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) {
-          const int d = lane + 32 * i;
-          if (d < dv) acc[a][i] = fmaf(pv, Vs[j * dv + d], acc[a][i]);
-        }
-      }
-    }
-  }
-#pragma unroll
-  for (int a = 0; a < MAX_HPW; ++a) {
-    const int g = warp + a * W;
-    if (g >= G) break;
-    float la = l[a], corr = 1.f;
-    if (sink != nullptr) {                  // the sink: one more term of the denominator, no value
-      const float sk = sink[head0 + g];
-      const float mn = fmaxf(m[a], sk);
-      corr = expf(m[a] - mn);
-      la = la * corr + expf(sk - mn);
-    }
-    const float inv = 1.0f / la;
+  for (int i = 0; i < DPL; ++i) acc[i] *= corr;
+  for (int j = 0; j < CHUNK; ++j) {
+    const float pv = __shfl_sync(0xffffffffu, pj, j);
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
       const int d = lane + 32 * i;
-      if (d < dv) orow[g * dv + d] = Cvt<T>::from_f(acc[a][i] * corr * inv);
+      if (d < dv) acc[i] = fmaf(pv, Vs[j * dv + d], acc[i]);
     }
   }
 }
 
-// ------------------------------------------------------------------------------------------------ recurrent scans
-// The state of a head is a key_dim x value_dim matrix S. A thread owns DPT = 16 consecutive rows of one column; the R
-// lanes that share a column (R a power of two, R * 16 >= key_dim, neighbours in a warp) add their partial dot products
-// with shuffles. State layout in memory: (slots, heads, value_dim, R * 16), so a thread's 16 values are contiguous and a
-// warp reads one contiguous run; rows beyond key_dim stay zero. A block of 256 threads covers 256 / R columns of one
-// head of one portion and walks the portion's tokens in chunks of TCH, staged in shared memory by all threads.
-constexpr int DPT = 16;
-constexpr int TCH = 8;
-constexpr int SCAN_THREADS = 256;
+// The sink (one more term of the denominator, no value), the division and the store of one pair's result.
+template <typename T, int DPL>
+__device__ __forceinline__ void pair_finish(const AttnArgs& a, int n, int head, float m, float l, const float* acc) {
+  const int lane = threadIdx.x & 31;
+  float corr = 1.f;
+  if (a.sink != nullptr) {
+    const float sk = a.sink[head];
+    const float mn = fmaxf(m, sk);
+    corr = expf(m - mn);
+    l = l * corr + expf(sk - mn);
+  }
+  const float inv = 1.0f / l;
+  T* o = (T*)a.out + ((size_t)n * a.Hq + head) * a.dv;
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) {
+    const int d = lane + 32 * i;
+    if (d < a.dv) o[d] = Cvt<T>::from_f(acc[i] * corr * inv);
+  }
+}
 
+// grid (portions, tiles of rows_per_block rows, kv heads x slices of the group); block 32 * ATT_WARPS.
+template <typename T, int DPL>   // DPL: value dims per lane = ceil(dv / 32)
+__global__ void __launch_bounds__(32 * ATT_WARPS)
+sink_attention_tile_kernel(const AttnArgs a) {
+  fz_grid_launch_dependents();
+  const int s = blockIdx.x;
+  if (s == gridDim.x - 1) {                    // the block after the last portion's: rows of padding get zeros
+    fz_grid_wait();
+    if (blockIdx.y == 0 && blockIdx.z == 0)
+      for (int n = 0; n < a.N; ++n)
+        if (a.seq_row[n] < 0)
+          for (int i = threadIdx.x; i < a.Hq * a.dv; i += blockDim.x) ((T*)a.out)[(size_t)n * a.Hq * a.dv + i] = Cvt<T>::from_f(0.f);
+    return;
+  }
+  const int row0 = a.seg[4 * s], cnt = a.seg[4 * s + 1], pos0 = a.seg[4 * s + 2];
+  fz_grid_wait();
+  const int r0 = blockIdx.y * a.rows_per_block;
+  if (r0 >= cnt) return;
+  extern __shared__ float smem[];
+  const int G_all = a.Hq / a.Hkv, slices = (G_all + MAX_PAIRS - 1) / MAX_PAIRS;
+  const int kvh = blockIdx.z / slices, g_base = (blockIdx.z % slices) * MAX_PAIRS;
+  const int G = min(MAX_PAIRS, G_all - g_base);
+  const int nr = min(a.rows_per_block, cnt - r0);
+  const int warp = threadIdx.x >> 5;
+  const int dk = a.dk, dv = a.dv;
+  float* Ks = smem;                            // [CHUNK][dk + 1]
+  float* Vs = Ks + CHUNK * (dk + 1);           // [CHUNK][dv]
+  float* Qs = Vs + CHUNK * dv;                 // [nr * G][dk]
+  const int head0 = kvh * G_all + g_base;
+  const T* q = (const T*)a.q;
+  for (int e = threadIdx.x; e < nr * G * dk; e += blockDim.x) {
+    const int pr = e / dk, d = e - pr * dk;
+    Qs[e] = Cvt<T>::to_f(q[((size_t)(row0 + r0 + pr / G) * a.Hq + head0 + pr % G) * dk + d]);
+  }
+  float m[MAX_PPW], l[MAX_PPW], acc[MAX_PPW][DPL];
+#pragma unroll
+  for (int x = 0; x < MAX_PPW; ++x) {
+    m[x] = -INFINITY;
+    l[x] = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[x][i] = 0.f;
+  }
+  const int p_first = pos0 + r0, p_last = p_first + nr - 1;
+  const ChunkWalk walk(p_first, p_last, a.window, a.keep_first);
+  const int* trow = a.table + (size_t)a.seq_row[row0] * a.mb;
+  const int pairs = nr * G;
+  for (int it = 0; it < walk.count; ++it) {
+    const int c = walk.chunk(it);
+    __syncthreads();   // the previous chunk is consumed (and Qs is written, the first time)
+    load_chunk<T>(a, trow, kvh, c, walk.lo, a.keep_first, p_last, Ks, Vs);
+    __syncthreads();
+#pragma unroll
+    for (int x = 0; x < MAX_PPW; ++x) {
+      const int pr = warp + x * ATT_WARPS;
+      if (pr >= pairs) break;
+      const int p = p_first + pr / G;
+      const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+      pair_chunk<DPL>(Qs + pr * dk, Ks, Vs, c, p, lo, a.keep_first, a.scale, dk, dv, m[x], l[x], acc[x]);
+    }
+  }
+#pragma unroll
+  for (int x = 0; x < MAX_PPW; ++x) {
+    const int pr = warp + x * ATT_WARPS;
+    if (pr >= pairs) break;
+    pair_finish<T, DPL>(a, row0 + r0 + pr / G, head0 + pr % G, m[x], l[x], acc[x]);
+  }
+}
+
+// grid (rows, kv heads x slices of the group, runs); a block walks `unit_chunks` chunks of its row and leaves, per query
+// head, (m, l, acc[dv]) at part[((n Hq + head) max_units + run) (dv + 2)]. Rows of padding and runs past the row's last
+// chunk leave nothing.
+template <typename T, int DPL>
+__global__ void __launch_bounds__(32 * ATT_WARPS)
+sink_attention_unit_kernel(const AttnArgs a) {
+  fz_grid_launch_dependents();
+  const int n = blockIdx.x;
+  const int row = a.seq_row[n], p = a.pos[n];
+  fz_grid_wait();
+  if (row < 0) return;
+  const ChunkWalk walk(p, p, a.window, a.keep_first);
+  const int it0 = blockIdx.z * a.unit_chunks;
+  if (it0 >= walk.count) return;
+  extern __shared__ float smem[];
+  const int G_all = a.Hq / a.Hkv, slices = (G_all + MAX_PAIRS - 1) / MAX_PAIRS;
+  const int kvh = blockIdx.y / slices, g_base = (blockIdx.y % slices) * MAX_PAIRS;
+  const int G = min(MAX_PAIRS, G_all - g_base);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int dk = a.dk, dv = a.dv;
+  float* Ks = smem;
+  float* Vs = Ks + CHUNK * (dk + 1);
+  float* Qs = Vs + CHUNK * dv;                 // [G][dk]
+  const int head0 = kvh * G_all + g_base;
+  const T* q = (const T*)a.q + ((size_t)n * a.Hq + head0) * dk;
+  for (int e = threadIdx.x; e < G * dk; e += blockDim.x) Qs[e] = Cvt<T>::to_f(q[e]);
+  float m[MAX_PPW], l[MAX_PPW], acc[MAX_PPW][DPL];
+#pragma unroll
+  for (int x = 0; x < MAX_PPW; ++x) {
+    m[x] = -INFINITY;
+    l[x] = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[x][i] = 0.f;
+  }
+  const int* trow = a.table + (size_t)row * a.mb;
+  for (int it = it0; it < min(walk.count, it0 + a.unit_chunks); ++it) {
+    const int c = walk.chunk(it);
+    __syncthreads();
+    load_chunk<T>(a, trow, kvh, c, walk.lo, a.keep_first, p, Ks, Vs);
+    __syncthreads();
+#pragma unroll
+    for (int x = 0; x < MAX_PPW; ++x) {
+      const int g = warp + x * ATT_WARPS;
+      if (g >= G) break;
+      pair_chunk<DPL>(Qs + g * dk, Ks, Vs, c, p, walk.lo, a.keep_first, a.scale, dk, dv, m[x], l[x], acc[x]);
+    }
+  }
+#pragma unroll
+  for (int x = 0; x < MAX_PPW; ++x) {
+    const int g = warp + x * ATT_WARPS;
+    if (g >= G) break;
+    float* o = a.part + (((size_t)n * a.Hq + head0 + g) * a.max_units + blockIdx.z) * (dv + 2);
+    if (lane == 0) { o[0] = m[x]; o[1] = l[x]; }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+      const int d = lane + 32 * i;
+      if (d < dv) o[2 + d] = acc[x][i];
+    }
+  }
+}
+
+// grid (rows, query heads), a warp each: the runs of a row in rising order, then the sink.
+template <typename T, int DPL>
+__global__ void __launch_bounds__(32)
+sink_attention_merge_kernel(const AttnArgs a) {
+  fz_grid_launch_dependents();
+  const int n = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
+  const int row = a.seq_row[n], p = a.pos[n];
+  fz_grid_wait();
+  const int dv = a.dv;
+  if (row < 0) {
+    T* o = (T*)a.out + ((size_t)n * a.Hq + head) * dv;
+    for (int d = lane; d < dv; d += 32) o[d] = Cvt<T>::from_f(0.f);
+    return;
+  }
+  const ChunkWalk walk(p, p, a.window, a.keep_first);
+  const int runs = (walk.count + a.unit_chunks - 1) / a.unit_chunks;
+  float m = -INFINITY, l = 0.f, acc[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+  for (int u = 0; u < runs; ++u) {
+    const float* o = a.part + (((size_t)n * a.Hq + head) * a.max_units + u) * (dv + 2);
+    const float mu = o[0], lu = o[1];
+    const float mn = fmaxf(m, mu);
+    if (mn == -INFINITY) continue;
+    const float ca = expf(m - mn), cb = expf(mu - mn);
+    l = l * ca + lu * cb;
+    m = mn;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+      const int d = lane + 32 * i;
+      if (d < dv) acc[i] = acc[i] * ca + o[2 + d] * cb;
+    }
+  }
+  pair_finish<T, DPL>(a, n, head, m, l, acc);
+}
+
+// ------------------------------------------------------------------------------------------------ recurrent scans
+// The state of a head is a key_dim x value_dim matrix S. A thread owns DPT = 16 consecutive rows of DC = 4 neighbouring
+// columns (64 values in registers: every key and query value it reads from shared memory serves four columns, and the
+// 64 independent chains hide the latencies of the token-by-token recurrence); the R lanes that share the columns (R a
+// power of two, R * 16 >= key_dim; lane = r * (32 / R) + group, so that the lanes of a quarter warp read one address)
+// add their partial dot products with shuffles. State layout in memory: (slots, heads, value_dim, R * 16), so a thread's 16 values are contiguous and a
+// column's run is read in 64-byte pieces; rows beyond key_dim stay zero. A block covers (blockDim / R) * 4 columns of one
+// head of one portion and walks the portion's tokens in chunks, staged in shared memory by all threads.
+constexpr int DPT = 16;
+constexpr int DC = 4;                       // value columns per thread
+constexpr int SCAN_MAX_THREADS = 256;
+// While a chunk of tokens is computed, the inputs of the next one travel from global into a raw staging area of shared
+// memory (`cp.async`, four bytes each); after the chunk they are turned into what the recurrence reads (rotated or unit
+// vectors, decays, gates) in a second area. tch: tokens per chunk (16, or 8 where shared memory would not hold 16).
+
+// Sum over the R lanes that hold the rows of one column group: they are 32 / R lanes apart.
 __device__ __forceinline__ float lanes_sum(float v, int R) {
-  for (int o = R >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  for (int o = 16; o >= 32 / R; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
+}
+
+// Which column group (of the block) and which 16 rows a thread owns.
+__device__ __forceinline__ void scan_place(int R, int& group, int& r) {
+  const int per_warp = 32 / R, lane = threadIdx.x & 31;
+  r = lane / per_warp;
+  group = (threadIdx.x >> 5) * per_warp + lane % per_warp;
 }
 
 __device__ __forceinline__ void load_state(const float* __restrict__ p, float* S) {
@@ -214,12 +383,28 @@ __device__ __forceinline__ void store_state(float* __restrict__ p, const float* 
   for (int i = 0; i < DPT; i += 4) *(float4*)(p + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
 }
 
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// Unit i of a run of values of T from global to shared: a four-byte copy in flight (T is float, or a pair of 16-bit
+// values where `words` says that source, destination and length allow it), else one value copied at once.
+template <typename T>
+__device__ __forceinline__ void stage_unit(T* dst, const T* src, int i, bool words) {
+  if (sizeof(T) == 4) cp_async4(dst + i, src + i);
+  else if (words) cp_async4(dst + 2 * i, src + 2 * i);
+  else dst[i] = src[i];
+}
+
 // S = decay * S + k' v^T; o = S^T q'. proj rows: [q heads | k heads | v heads | ...], ld floats apart.
-__global__ void __launch_bounds__(SCAN_THREADS)
-retention_scan_kernel(const float* __restrict__ proj, int ld, int H, int dk, int dv, int R, const float* __restrict__ decay,
-                      float key_scale, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rotated,
-                      int pairing, int max_pos, float* __restrict__ state, const int* __restrict__ seg,
-                      float* __restrict__ out, int* err) {
+__global__ void __launch_bounds__(SCAN_MAX_THREADS)
+retention_scan_kernel(const float* __restrict__ proj, int ld, int H, int dk, int dv, int R, int tch,
+                      const float* __restrict__ decay, float key_scale, const float* __restrict__ cos_t,
+                      const float* __restrict__ sin_t, int rotated, int pairing, int max_pos, float* __restrict__ state,
+                      const int* __restrict__ seg, float* __restrict__ out, int* err) {
   fz_grid_launch_dependents();
   const int s = blockIdx.x, h = blockIdx.y;
   const int row0 = seg[4 * s], cnt = seg[4 * s + 1], pos0 = seg[4 * s + 2], slot = seg[4 * s + 3];
@@ -227,100 +412,184 @@ retention_scan_kernel(const float* __restrict__ proj, int ld, int H, int dk, int
   if (cnt <= 0 || slot < 0) return;
   if (rotated > 0 && (pos0 < 0 || pos0 + cnt > max_pos)) { if (threadIdx.x == 0) atomicOr(err, FZ_ERR_POS_RANGE); return; }
   extern __shared__ float smem[];
-  const int dkp = R * DPT, COLS = SCAN_THREADS / R;
-  float* qs = smem;                    // [TCH][dkp]
-  float* ks = qs + TCH * dkp;          // [TCH][dkp]
-  float* vs = ks + TCH * dkp;          // [TCH][COLS]
-  const int cl = threadIdx.x / R, r = threadIdx.x - cl * R;
-  const int col = blockIdx.z * COLS + cl;
-  const bool live = col < dv;
-  float* sp = state + (((size_t)slot * H + h) * dv + (live ? col : 0)) * dkp + r * DPT;
-  float S[DPT];
-  if (live) load_state(sp, S);
-  else {
+  const int NT = blockDim.x;
+  const int dkp = R * DPT, COLS = NT / R * DC, half = rotated >> 1;
+  float* qs = smem;                    // [tch][dkp]   what the recurrence reads
+  float* ks = qs + tch * dkp;          // [tch][dkp]
+  float* vs = ks + tch * dkp;          // [tch][COLS]
+  float* rq = vs + tch * COLS;         // [tch][dk]    raw: as the projections left them
+  float* rk = rq + tch * dk;           // [tch][dk]
+  float* rv = rk + tch * dk;           // [tch][COLS]
+  float* rc = rv + tch * COLS;         // [tch][half]  the rows of the cosine and sine tables
+  float* rs = rc + tch * half;         // [tch][half]
+  int group, r;
+  scan_place(R, group, r);
+  const int col0 = blockIdx.z * COLS, col = col0 + group * DC;      // this thread's first column
+  const int ncols = min(COLS, dv - col0);
+  float* sp = state + (((size_t)slot * H + h) * dv + col) * dkp + r * DPT;
+  float S[DC][DPT];
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) S[i] = 0.f;
+  for (int j = 0; j < DC; ++j) {
+    if (col + j < dv) load_state(sp + (size_t)j * dkp, S[j]);
+    else {
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) S[j][i] = 0.f;
+    }
   }
   const float dec = decay[h];
-  const int half = rotated >> 1;
-  for (int t0 = 0; t0 < cnt; t0 += TCH) {
-    const int tc = min(TCH, cnt - t0);
-    __syncthreads();
-    for (int e = threadIdx.x; e < tc * dkp; e += SCAN_THREADS) {
+  const int per_token = 2 * dk + ncols + 2 * half;      // values a token brings: q, k, its columns of v, cosines, sines
+  auto issue = [&](int t0) {
+    const int tc = min(tch, cnt - t0);
+    for (int e = threadIdx.x; e < tc * per_token; e += NT) {
+      const int tt = e / per_token;
+      int i = e - tt * per_token;
+      const float* in = proj + (size_t)(row0 + t0 + tt) * ld;
+      if (i < dk) { cp_async4(rq + tt * dk + i, in + (size_t)h * dk + i); continue; }
+      i -= dk;
+      if (i < dk) { cp_async4(rk + tt * dk + i, in + (size_t)(H + h) * dk + i); continue; }
+      i -= dk;
+      if (i < ncols) { cp_async4(rv + tt * COLS + i, in + (size_t)2 * H * dk + (size_t)h * dv + col0 + i); continue; }
+      i -= ncols;
+      if (i < half) cp_async4(rc + tt * half + i, cos_t + (size_t)(pos0 + t0 + tt) * half + i);
+      else cp_async4(rs + tt * half + i - half, sin_t + (size_t)(pos0 + t0 + tt) * half + i - half);
+    }
+    cp_async_commit();
+  };
+  auto cook = [&](int t0) {
+    const int tc = min(tch, cnt - t0);
+    for (int e = threadIdx.x; e < tc * dkp; e += NT) {
       const int tt = e / dkp, i = e - tt * dkp;
       float qv = 0.f, kv = 0.f;
       if (i < dk) {
-        const float* in = proj + (size_t)(row0 + t0 + tt) * ld;
-        const size_t at = (size_t)(pos0 + t0 + tt) * half;
-        qv = rotated_value(in + (size_t)h * dk, i, rotated, pairing, cos_t + at, sin_t + at);
-        kv = __fmul_rn(rotated_value(in + (size_t)(H + h) * dk, i, rotated, pairing, cos_t + at, sin_t + at), key_scale);
+        qv = rotated_value(rq + tt * dk, i, rotated, pairing, rc + tt * half, rs + tt * half);
+        kv = __fmul_rn(rotated_value(rk + tt * dk, i, rotated, pairing, rc + tt * half, rs + tt * half), key_scale);
       }
       qs[e] = qv;
       ks[e] = kv;
     }
-    for (int e = threadIdx.x; e < tc * COLS; e += SCAN_THREADS) {
-      const int tt = e / COLS, c = e - tt * COLS;
-      const int cc = blockIdx.z * COLS + c;
-      vs[e] = cc < dv ? proj[(size_t)(row0 + t0 + tt) * ld + (size_t)2 * H * dk + (size_t)h * dv + cc] : 0.f;
+    for (int e = threadIdx.x; e < tc * COLS; e += NT) {
+      const int c = e % COLS;
+      vs[e] = c < ncols ? rv[e] : 0.f;
     }
-    __syncthreads();
+  };
+
+  issue(0);
+  cp_async_wait();
+  __syncthreads();
+  cook(0);
+  __syncthreads();
+  for (int t0 = 0; t0 < cnt; t0 += tch) {
+    const int tc = min(tch, cnt - t0);
+    const bool more = t0 + tch < cnt;
+    if (more) issue(t0 + tch);
     for (int tt = 0; tt < tc; ++tt) {
-      const float v = vs[tt * COLS + cl];
+      const float4 v4 = *(const float4*)(vs + tt * COLS + group * DC);
+      const float v[DC] = {v4.x, v4.y, v4.z, v4.w};
       const float* kk = ks + tt * dkp + r * DPT;
       const float* qq = qs + tt * dkp + r * DPT;
-      float o = 0.f;
+      float o[DC] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {
-        S[i] = __fmaf_rn(dec, S[i], __fmul_rn(kk[i], v));
-        o = __fmaf_rn(S[i], qq[i], o);
+        const float ki = kk[i], qi = qq[i];
+#pragma unroll
+        for (int j = 0; j < DC; ++j) {
+          S[j][i] = __fmaf_rn(dec, S[j][i], __fmul_rn(ki, v[j]));
+          o[j] = __fmaf_rn(S[j][i], qi, o[j]);
+        }
       }
-      o = lanes_sum(o, R);
-      if (live && r == 0) out[(size_t)(row0 + t0 + tt) * H * dv + (size_t)h * dv + col] = o;
+#pragma unroll
+      for (int j = 0; j < DC; ++j) o[j] = lanes_sum(o[j], R);
+      if (r == 0) {
+        float* dst = out + (size_t)(row0 + t0 + tt) * H * dv + (size_t)h * dv + col;
+#pragma unroll
+        for (int j = 0; j < DC; ++j)
+          if (col + j < dv) dst[j] = o[j];
+      }
+    }
+    if (more) {
+      cp_async_wait();
+      __syncthreads();               // the next chunk's raw inputs have arrived; every thread is done with this chunk
+      cook(t0 + tch);
+      __syncthreads();
     }
   }
-  if (live) store_state(sp, S);
+#pragma unroll
+  for (int j = 0; j < DC; ++j)
+    if (col + j < dv) store_state(sp + (size_t)j * dkp, S[j]);
 }
 
 // S = g * S (rows); u = beta (v - S^T k^); S += k^ u^T; o = S^T q^. qkv rows: [q (Hk dk) | k (Hk dk) | v (H dv)] of T.
 template <typename T>
-__global__ void __launch_bounds__(SCAN_THREADS)
-gated_delta_scan_kernel(const T* __restrict__ qkv, int H, int Hk, int dk, int dv, int R, const float* __restrict__ high,
-                        int ldh, const float* __restrict__ beta, const float* __restrict__ a_log,
-                        const float* __restrict__ dt_bias, float unit_eps, float q_scale, float* __restrict__ state,
-                        const int* __restrict__ seg, float* __restrict__ out) {
+__global__ void __launch_bounds__(SCAN_MAX_THREADS)
+gated_delta_scan_kernel(const T* __restrict__ qkv, int H, int Hk, int dk, int dv, int R, int tch,
+                        const float* __restrict__ high, int ldh, const float* __restrict__ beta,
+                        const float* __restrict__ a_log, const float* __restrict__ dt_bias, float unit_eps, float q_scale,
+                        float* __restrict__ state, const int* __restrict__ seg, float* __restrict__ out) {
   fz_grid_launch_dependents();
   const int s = blockIdx.x, h = blockIdx.y;
   const int row0 = seg[4 * s], cnt = seg[4 * s + 1], slot = seg[4 * s + 3];
   fz_grid_wait();
   if (cnt <= 0 || slot < 0) return;
   extern __shared__ float smem[];
-  const int dkp = R * DPT, COLS = SCAN_THREADS / R;
-  float* qs = smem;                    // [TCH][dkp]
-  float* ks = qs + TCH * dkp;
-  float* gs = ks + TCH * dkp;
-  float* vs = gs + TCH * dkp;          // [TCH][COLS]
-  float* bs = vs + TCH * COLS;         // [TCH]
-  const int cl = threadIdx.x / R, r = threadIdx.x - cl * R;
-  const int col = blockIdx.z * COLS + cl;
-  const bool live = col < dv;
+  const int NT = blockDim.x;
+  const int dkp = R * DPT, COLS = NT / R * DC;
+  const int dke = (dk + 1) & ~1, cole = (COLS + 1) & ~1;      // raw rows of T start on four-byte boundaries
+  float* qs = smem;                    // [tch][dkp]   what the recurrence reads
+  float* ks = qs + tch * dkp;
+  float* gs = ks + tch * dkp;
+  float* vs = gs + tch * dkp;          // [tch][COLS]
+  float* bs = vs + tch * COLS;         // [tch]
+  float* ra = bs + tch;                // [tch][dk]    raw: decay inputs
+  float* rb = ra + tch * dk;           // [tch]        raw: beta before the sigmoid
+  T* rq = (T*)(rb + tch);              // [tch][dke]   raw: q, k, v after the convolution
+  T* rk = rq + tch * dke;
+  T* rv = rk + tch * dke;              // [tch][cole]
+  int group, r;
+  scan_place(R, group, r);
+  const int col0 = blockIdx.z * COLS, col = col0 + group * DC;      // this thread's first column
+  const int ncols = min(COLS, dv - col0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kh = h / (H / Hk);
   const int C = 2 * Hk * dk + H * dv;
-  float* sp = state + (((size_t)slot * H + h) * dv + (live ? col : 0)) * dkp + r * DPT;
-  float S[DPT];
-  if (live) load_state(sp, S);
-  else {
+  // 16-bit values travel in pairs where every run starts on a four-byte boundary and has an even length
+  const bool words = sizeof(T) == 4 || (((dk | dv | C | col0 | ncols) & 1) == 0 && ((uintptr_t)qkv & 3) == 0);
+  float* sp = state + (((size_t)slot * H + h) * dv + col) * dkp + r * DPT;
+  float S[DC][DPT];
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) S[i] = 0.f;
+  for (int j = 0; j < DC; ++j) {
+    if (col + j < dv) load_state(sp + (size_t)j * dkp, S[j]);
+    else {
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) S[j][i] = 0.f;
+    }
   }
   const float rate = expf(a_log[h]);
-  for (int t0 = 0; t0 < cnt; t0 += TCH) {
-    const int tc = min(TCH, cnt - t0);
-    __syncthreads();
-    for (int tt = warp; tt < tc; tt += SCAN_THREADS / 32) {      // a warp stages a token: unit vectors, decays, beta
+  const bool pairs = sizeof(T) == 2 && words;
+  const int uq = pairs ? dk / 2 : dk, uv = pairs ? ncols / 2 : ncols;      // copies per run of q or k, and of v
+  const int per_token = 2 * uq + uv + dk + 1;
+  auto issue = [&](int t0) {
+    const int tc = min(tch, cnt - t0);
+    for (int e = threadIdx.x; e < tc * per_token; e += NT) {
+      const int tt = e / per_token;
+      int i = e - tt * per_token;
       const size_t n = (size_t)(row0 + t0 + tt);
-      const T* qin = qkv + n * C + (size_t)kh * dk;
-      const T* kin = qin + (size_t)Hk * dk;
+      const T* in = qkv + n * C;
+      if (i < uq) { stage_unit(rq + tt * dke, in + (size_t)kh * dk, i, words); continue; }
+      i -= uq;
+      if (i < uq) { stage_unit(rk + tt * dke, in + (size_t)(Hk + kh) * dk, i, words); continue; }
+      i -= uq;
+      if (i < uv) { stage_unit(rv + tt * cole, in + (size_t)2 * Hk * dk + (size_t)h * dv + col0, i, words); continue; }
+      i -= uv;
+      if (i < dk) cp_async4(ra + tt * dk + i, high + n * ldh + (size_t)h * dk + i);
+      else cp_async4(rb + tt, beta + n * H + h);
+    }
+    cp_async_commit();
+  };
+  auto cook = [&](int t0) {
+    const int tc = min(tch, cnt - t0);
+    for (int tt = warp; tt < tc; tt += NT / 32) {      // a warp cooks a token: unit vectors, decays, beta
+      const T* qin = rq + tt * dke;
+      const T* kin = rk + tt * dke;
       float sq = 0.f, sk = 0.f;
       for (int i = lane; i < dk; i += 32) {
         const float a = Cvt<T>::to_f(qin[i]), b = Cvt<T>::to_f(kin[i]);
@@ -333,7 +602,7 @@ gated_delta_scan_kernel(const T* __restrict__ qkv, int H, int Hk, int dk, int dv
         if (i < dk) {
           qv = __fmul_rn(__fdiv_rn(Cvt<T>::to_f(qin[i]), nq), q_scale);
           kv = __fdiv_rn(Cvt<T>::to_f(kin[i]), nk);
-          const float a = high[n * ldh + (size_t)h * dk + i] + dt_bias[(size_t)h * dk + i];
+          const float a = ra[tt * dk + i] + dt_bias[(size_t)h * dk + i];
           const float soft = a > 20.f ? a : log1pf(expf(a));
           gv = expf(-rate * soft);
         }
@@ -341,38 +610,71 @@ gated_delta_scan_kernel(const T* __restrict__ qkv, int H, int Hk, int dk, int dv
         ks[tt * dkp + i] = kv;
         gs[tt * dkp + i] = gv;
       }
-      if (lane == 0) bs[tt] = 1.0f / (1.0f + expf(-beta[n * H + h]));
+      if (lane == 0) bs[tt] = 1.0f / (1.0f + expf(-rb[tt]));
     }
-    for (int e = threadIdx.x; e < tc * COLS; e += SCAN_THREADS) {
+    for (int e = threadIdx.x; e < tc * COLS; e += NT) {
       const int tt = e / COLS, c = e - tt * COLS;
-      const int cc = blockIdx.z * COLS + c;
-      vs[e] = cc < dv ? Cvt<T>::to_f(qkv[(size_t)(row0 + t0 + tt) * C + (size_t)2 * Hk * dk + (size_t)h * dv + cc]) : 0.f;
+      vs[e] = c < ncols ? Cvt<T>::to_f(rv[tt * cole + c]) : 0.f;
     }
-    __syncthreads();
+  };
+
+  issue(0);
+  cp_async_wait();
+  __syncthreads();
+  cook(0);
+  __syncthreads();
+  for (int t0 = 0; t0 < cnt; t0 += tch) {
+    const int tc = min(tch, cnt - t0);
+    const bool more = t0 + tch < cnt;
+    if (more) issue(t0 + tch);
     for (int tt = 0; tt < tc; ++tt) {
-      const float v = vs[tt * COLS + cl], b = bs[tt];
+      const float4 v4 = *(const float4*)(vs + tt * COLS + group * DC);
+      const float v[DC] = {v4.x, v4.y, v4.z, v4.w};
+      const float b = bs[tt];
       const float* kk = ks + tt * dkp + r * DPT;
       const float* qq = qs + tt * dkp + r * DPT;
       const float* gg = gs + tt * dkp + r * DPT;
-      float ksum = 0.f;
+      float ksum[DC] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {
-        S[i] = __fmul_rn(gg[i], S[i]);
-        ksum = __fmaf_rn(S[i], kk[i], ksum);
+        const float gi = gg[i], ki = kk[i];
+#pragma unroll
+        for (int j = 0; j < DC; ++j) {
+          S[j][i] = __fmul_rn(gi, S[j][i]);
+          ksum[j] = __fmaf_rn(S[j][i], ki, ksum[j]);
+        }
       }
-      ksum = lanes_sum(ksum, R);
-      const float u = __fmul_rn(b, v - ksum);
-      float o = 0.f;
+      float u[DC], o[DC] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < DC; ++j) u[j] = __fmul_rn(b, v[j] - lanes_sum(ksum[j], R));
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {
-        S[i] = __fmaf_rn(kk[i], u, S[i]);
-        o = __fmaf_rn(S[i], qq[i], o);
+        const float ki = kk[i], qi = qq[i];
+#pragma unroll
+        for (int j = 0; j < DC; ++j) {
+          S[j][i] = __fmaf_rn(ki, u[j], S[j][i]);
+          o[j] = __fmaf_rn(S[j][i], qi, o[j]);
+        }
       }
-      o = lanes_sum(o, R);
-      if (live && r == 0) out[(size_t)(row0 + t0 + tt) * H * dv + (size_t)h * dv + col] = o;
+#pragma unroll
+      for (int j = 0; j < DC; ++j) o[j] = lanes_sum(o[j], R);
+      if (r == 0) {
+        float* dst = out + (size_t)(row0 + t0 + tt) * H * dv + (size_t)h * dv + col;
+#pragma unroll
+        for (int j = 0; j < DC; ++j)
+          if (col + j < dv) dst[j] = o[j];
+      }
+    }
+    if (more) {
+      cp_async_wait();
+      __syncthreads();
+      cook(t0 + tch);
+      __syncthreads();
     }
   }
-  if (live) store_state(sp, S);
+#pragma unroll
+  for (int j = 0; j < DC; ++j)
+    if (col + j < dv) store_state(sp + (size_t)j * dkp, S[j]);
 }
 
 // out[n, h, c] = o / sqrt(mean_c o^2 + eps) * w[c] * act(gate[n, goff + h dv + c]); a warp per (row, head).
@@ -522,37 +824,53 @@ int lanes_per_column(int dk) {
   return R;
 }
 
-template <typename T, int DPL>
-int launch_sink(const void* q, const void* k_pool, const void* v_pool, const int* pos, const int* seq_row, const int* table,
-                int mb, long long page_stride, long long head_stride, long long tok_stride, int page_size, int n_pages,
-                void* out, int N, int Hq, int Hkv, int dk, int dv, float scale, int window, int keep_first,
-                const float* sink, int* err, cudaStream_t stream) {
-  const int G_all = Hq / Hkv, G = G_all < MAX_GROUP ? G_all : MAX_GROUP;
-  const int W = G < MAX_WARPS ? G : MAX_WARPS;
-  const size_t smem = sizeof(float) * ((size_t)CHUNK * (dk + 1) + (size_t)CHUNK * dv + (size_t)G * dk);
-  auto kern = sink_attention_kernel<T, DPL>;
-  static size_t allowed = 48 * 1024;
+size_t attn_smem(int dk, int dv, int pairs) {
+  return sizeof(float) * ((size_t)CHUNK * (dk + 1) + (size_t)CHUNK * dv + (size_t)pairs * dk);
+}
+
+template <typename K>
+int allow_smem(K kern, size_t smem, size_t& allowed) {
   if (smem > allowed) {
     if (smem > 227 * 1024) return FZ_TOO_LARGE;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     allowed = smem;
   }
-  dim3 grid(N, Hkv, (G_all + MAX_GROUP - 1) / MAX_GROUP);
-  fz_launch(kern, grid, dim3(32 * W), smem, stream, (const T*)q, (const T*)k_pool, (const T*)v_pool, pos, seq_row, table, mb,
-            page_stride, head_stride, tok_stride, page_size, n_pages, (T*)out, Hq, Hkv, dk, dv, scale, window, keep_first,
-            sink, err);
+  return FZ_OK;
+}
+
+// rows_per_block: as many rows of a portion as give 32 (row, head) pairs at most.
+template <typename T, int DPL>
+int launch_sink(AttnArgs a, int N, int n_seg, int max_portion, int units, cudaStream_t stream) {
+  const int G_all = a.Hq / a.Hkv, slices = (G_all + MAX_PAIRS - 1) / MAX_PAIRS;
+  const int G = G_all < MAX_PAIRS ? G_all : MAX_PAIRS;
+  if (units > 0) {                      // single tokens: runs of chunks per block, then the merge
+    static size_t allowed_u = 48 * 1024;
+    const size_t smem = attn_smem(a.dk, a.dv, G);
+    int st = allow_smem(sink_attention_unit_kernel<T, DPL>, smem, allowed_u);
+    if (st != FZ_OK) return st;
+    fz_launch(sink_attention_unit_kernel<T, DPL>, dim3(N, a.Hkv * slices, units), dim3(32 * ATT_WARPS), smem, stream, a);
+    FZ_LAUNCH_CHECK();
+    fz_launch(sink_attention_merge_kernel<T, DPL>, dim3(N, a.Hq), dim3(32), 0, stream, a);
+    FZ_LAUNCH_CHECK();
+    return FZ_OK;
+  }
+  a.rows_per_block = MAX_PAIRS / G > 0 ? MAX_PAIRS / G : 1;
+  static size_t allowed_t = 48 * 1024;
+  const size_t smem = attn_smem(a.dk, a.dv, a.rows_per_block * G);
+  int st = allow_smem(sink_attention_tile_kernel<T, DPL>, smem, allowed_t);
+  if (st != FZ_OK) return st;
+  const int tiles = (max_portion + a.rows_per_block - 1) / a.rows_per_block;
+  if (tiles > 65535 || a.Hkv * slices > 65535) return FZ_TOO_LARGE;
+  fz_launch(sink_attention_tile_kernel<T, DPL>, dim3(n_seg + 1, tiles, a.Hkv * slices), dim3(32 * ATT_WARPS), smem, stream, a);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }
 
 template <typename T>
-int dispatch_sink(const void* q, const void* k_pool, const void* v_pool, const int* pos, const int* seq_row,
-                  const int* table, int mb, long long page_stride, long long head_stride, long long tok_stride,
-                  int page_size, int n_pages, void* out, int N, int Hq, int Hkv, int dk, int dv, float scale, int window,
-                  int keep_first, const float* sink, int* err, cudaStream_t stream) {
-#define FZ_GO(D) return launch_sink<T, D>(q, k_pool, v_pool, pos, seq_row, table, mb, page_stride, head_stride, tok_stride, page_size, n_pages, out, N, Hq, Hkv, dk, dv, scale, window, keep_first, sink, err, stream)
-  const int dpl = (dv + 31) / 32;
+int dispatch_sink(const AttnArgs& a, int N, int n_seg, int max_portion, int units, cudaStream_t stream) {
+#define FZ_GO(D) return launch_sink<T, D>(a, N, n_seg, max_portion, units, stream)
+  const int dpl = (a.dv + 31) / 32;
   if (dpl <= 1) FZ_GO(1);
   if (dpl <= 2) FZ_GO(2);
   if (dpl <= 4) FZ_GO(4);
@@ -586,22 +904,31 @@ FZ_API int fz_rotate_kv_write(const float* qkv, const float* cos_t, const float*
 // Sizes taken: Hq any multiple of Hkv, 0 < dk, dv <= 512.
 FZ_API int fz_sink_attention_check(int Hq, int Hkv, int dk, int dv) {
   if (Hq <= 0 || Hkv <= 0 || dk <= 0 || dv <= 0 || Hq % Hkv || dk > 512 || dv > 512 || Hkv > 65535) return FZ_BAD_SHAPE;
-  if ((Hq / Hkv + MAX_GROUP - 1) / MAX_GROUP > 65535) return FZ_BAD_SHAPE;
   return FZ_OK;
 }
 
+// How many runs of `unit_chunks` chunks a row can have at most, for contexts up to max_context.
+FZ_API int fz_sink_attention_units(int window, int keep_first, int max_context, int unit_chunks) {
+  const int keys = window > 0 ? (window < max_context ? window : max_context) : max_context;
+  const int kept = window > 0 ? (keep_first < max_context ? keep_first : max_context) : 0;
+  const int chunks = (keys + CHUNK - 1) / CHUNK + 1 + (kept + CHUNK - 1) / CHUNK;
+  return (chunks + unit_chunks - 1) / unit_chunks;
+}
+
+// Portions are rows of `seg` (n_seg of them, max_portion rows at most). units > 0 (every portion a single token): the
+// keys of a row are cut into runs of unit_chunks chunks, `units` at most, with `part` of N * Hq * units * (dv + 2) floats.
 FZ_API int fz_sink_attention(const void* q, const void* k_pool, const void* v_pool, const int* pos, const int* seq_row,
-                             const int* table, int mb, long long page_stride, long long head_stride, long long tok_stride,
-                             int page_size, int n_pages, void* out, int dtype, int N, int Hq, int Hkv, int dk, int dv,
-                             float scale, int window, int keep_first, const float* sink, int* err, cudaStream_t stream) {
-  if (N <= 0) return FZ_OK;
-  if (fz_sink_attention_check(Hq, Hkv, dk, dv) != FZ_OK || page_size <= 0 || window < 0 || keep_first < 0) return FZ_BAD_SHAPE;
-  if (dtype == FZ_F32)
-    return dispatch_sink<float>(q, k_pool, v_pool, pos, seq_row, table, mb, page_stride, head_stride, tok_stride, page_size,
-                                n_pages, out, N, Hq, Hkv, dk, dv, scale, window, keep_first, sink, err, stream);
-  if (dtype == FZ_BF16)
-    return dispatch_sink<__nv_bfloat16>(q, k_pool, v_pool, pos, seq_row, table, mb, page_stride, head_stride, tok_stride,
-                                        page_size, n_pages, out, N, Hq, Hkv, dk, dv, scale, window, keep_first, sink, err, stream);
+                             const int* seg, int n_seg, int max_portion, const int* table, int mb, long long page_stride,
+                             long long head_stride, long long tok_stride, int page_size, int n_pages, void* out, int dtype,
+                             int N, int Hq, int Hkv, int dk, int dv, float scale, int window, int keep_first,
+                             const float* sink, int unit_chunks, int units, float* part, int* err, cudaStream_t stream) {
+  if (N <= 0 || n_seg <= 0) return FZ_OK;
+  if (fz_sink_attention_check(Hq, Hkv, dk, dv) != FZ_OK || page_size <= 0 || window < 0 || keep_first < 0 || max_portion <= 0 ||
+      (units > 0 && (unit_chunks <= 0 || part == nullptr || units > 65535))) return FZ_BAD_SHAPE;
+  AttnArgs a = {q, k_pool, v_pool, pos, seq_row, seg, table, mb, page_stride, head_stride, tok_stride, page_size, n_pages, out,
+                Hq, Hkv, dk, dv, scale, window, keep_first, sink, err, N, 1, unit_chunks, units, part};
+  if (dtype == FZ_F32) return dispatch_sink<float>(a, N, n_seg, max_portion, units, stream);
+  if (dtype == FZ_BF16) return dispatch_sink<__nv_bfloat16>(a, N, n_seg, max_portion, units, stream);
   return FZ_BAD_DTYPE;
 }
 
@@ -611,15 +938,50 @@ FZ_API int fz_recurrent_key_pad(int dk) {
   return lanes_per_column(dk) * DPT;
 }
 
+// Shared memory of a scan with `tch` tokens per chunk (floats): what the recurrence reads, then the raw staging area.
+// Threads of a scan block: R lanes for each group of DC of the head's value columns, a multiple of 32, SCAN_MAX_THREADS at most.
+static int scan_threads(int dv, int R) {
+  const long long want = ((long long)((dv + DC - 1) / DC) * R + 31) / 32 * 32;
+  return (int)(want < SCAN_MAX_THREADS ? want : SCAN_MAX_THREADS);
+}
+static size_t retention_smem(int dk, int R, int cols, int rotated, int tch) {
+  const int dkp = R * DPT;
+  return sizeof(float) * (size_t)tch * ((size_t)2 * dkp + cols + 2 * dk + cols + rotated);
+}
+static size_t delta_smem(int dk, int R, int cols, int tch, size_t elem) {
+  const int dkp = R * DPT;
+  return sizeof(float) * (size_t)tch * ((size_t)3 * dkp + cols + 1 + dk + 1) + elem * (size_t)tch * (2 * ((dk + 1) & ~1) + ((cols + 1) & ~1)) + 16;
+}
+
 FZ_API int fz_retention_scan(const float* proj, int ld, int H, int dk, int dv, const float* decay, float key_scale,
                              const float* cos_t, const float* sin_t, int rotated, int pairing, int max_pos, float* state,
                              const int* seg, int n_seg, float* out, int* err, cudaStream_t stream) {
   if (n_seg <= 0) return FZ_OK;
   if (H <= 0 || H > 65535 || dv <= 0 || fz_recurrent_key_pad(dk) < 0 || rotated < 0 || rotated > dk || (rotated & 1)) return FZ_BAD_SHAPE;
-  const int R = lanes_per_column(dk), cols = SCAN_THREADS / R;
-  const size_t smem = sizeof(float) * ((size_t)2 * TCH * R * DPT + (size_t)TCH * cols);
-  fz_launch(retention_scan_kernel, dim3(n_seg, H, (dv + cols - 1) / cols), dim3(SCAN_THREADS), smem, stream, proj, ld, H, dk, dv,
-            R, decay, key_scale, cos_t, sin_t, rotated, pairing, max_pos, state, seg, out, err);
+  const int R = lanes_per_column(dk), threads = scan_threads(dv, R), cols = threads / R * DC;
+  const int tch = retention_smem(dk, R, cols, rotated, 16) <= 48 * 1024 ? 16 : 8;
+  const size_t smem = retention_smem(dk, R, cols, rotated, tch);
+  static size_t allowed = 48 * 1024;
+  int st = allow_smem(retention_scan_kernel, smem, allowed);
+  if (st != FZ_OK) return st;
+  fz_launch(retention_scan_kernel, dim3(n_seg, H, (dv + cols - 1) / cols), dim3(threads), smem, stream, proj, ld, H, dk, dv,
+            R, tch, decay, key_scale, cos_t, sin_t, rotated, pairing, max_pos, state, seg, out, err);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+template <typename T>
+static int launch_delta(const void* qkv, int H, int Hk, int dk, int dv, const float* high, int ldh, const float* beta,
+                        const float* a_log, const float* dt_bias, float unit_eps, float q_scale, float* state, const int* seg,
+                        int n_seg, float* out, cudaStream_t stream) {
+  const int R = lanes_per_column(dk), threads = scan_threads(dv, R), cols = threads / R * DC;
+  const int tch = delta_smem(dk, R, cols, 16, sizeof(T)) <= 48 * 1024 ? 16 : 8;
+  const size_t smem = delta_smem(dk, R, cols, tch, sizeof(T));
+  static size_t allowed = 48 * 1024;
+  int st = allow_smem(gated_delta_scan_kernel<T>, smem, allowed);
+  if (st != FZ_OK) return st;
+  fz_launch(gated_delta_scan_kernel<T>, dim3(n_seg, H, (dv + cols - 1) / cols), dim3(threads), smem, stream, (const T*)qkv,
+            H, Hk, dk, dv, R, tch, high, ldh, beta, a_log, dt_bias, unit_eps, q_scale, state, seg, out);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }
@@ -629,19 +991,11 @@ FZ_API int fz_gated_delta_scan(const void* qkv, int dtype, int H, int Hk, int dk
                                float* state, const int* seg, int n_seg, float* out, cudaStream_t stream) {
   if (n_seg <= 0) return FZ_OK;
   if (H <= 0 || H > 65535 || Hk <= 0 || H % Hk || dv <= 0 || fz_recurrent_key_pad(dk) < 0) return FZ_BAD_SHAPE;
-  const int R = lanes_per_column(dk), cols = SCAN_THREADS / R;
-  const size_t smem = sizeof(float) * ((size_t)3 * TCH * R * DPT + (size_t)TCH * cols + TCH);
-  if (smem > 48 * 1024) return FZ_TOO_LARGE;
-  const dim3 grid(n_seg, H, (dv + cols - 1) / cols);
   if (dtype == FZ_F32)
-    fz_launch(gated_delta_scan_kernel<float>, grid, dim3(SCAN_THREADS), smem, stream, (const float*)qkv, H, Hk, dk, dv, R, high,
-              ldh, beta, a_log, dt_bias, unit_eps, q_scale, state, seg, out);
-  else if (dtype == FZ_BF16)
-    fz_launch(gated_delta_scan_kernel<__nv_bfloat16>, grid, dim3(SCAN_THREADS), smem, stream, (const __nv_bfloat16*)qkv, H, Hk,
-              dk, dv, R, high, ldh, beta, a_log, dt_bias, unit_eps, q_scale, state, seg, out);
-  else return FZ_BAD_DTYPE;
-  FZ_LAUNCH_CHECK();
-  return FZ_OK;
+    return launch_delta<float>(qkv, H, Hk, dk, dv, high, ldh, beta, a_log, dt_bias, unit_eps, q_scale, state, seg, n_seg, out, stream);
+  if (dtype == FZ_BF16)
+    return launch_delta<__nv_bfloat16>(qkv, H, Hk, dk, dv, high, ldh, beta, a_log, dt_bias, unit_eps, q_scale, state, seg, n_seg, out, stream);
+  return FZ_BAD_DTYPE;
 }
 
 // act: 0 none, 1 sigmoid, 2 silu.

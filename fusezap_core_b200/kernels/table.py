@@ -134,6 +134,7 @@ class CudaOps(Ops):
         self.cut_prefill_keys = True       # few query tiles with many keys behind them are cut along the keys
         self._profile = None               # a StepProfile while the engine profiles its steps
         self._meta_rows = None             # meta.seq_row of the step being run, for ops that take no `meta`
+        self.split_decode_keys = True      # windowed attention with a sink: steps of single tokens cut a row's keys into runs
         # the fewest query heads, and the fewest items of a query tile on the prompt kernel, among the attention layers
         # that `check_attention` has seen (the plan of a step is shared by its layers)
         self._attn_heads = self._attn_items = 0
@@ -261,6 +262,8 @@ class CudaOps(Ops):
     def plan_step(self, meta, needs: tuple) -> None:
         """Called when a step has been packed on the host, before its one copy to the device: writes the attention
         kernels' tile list into the block's extra part and keeps the launch sizes in `meta.plan`."""
+        # kernels that tile the rows of portions size their grid by the longest portion
+        meta.portion_tiles = int(meta.max_portion) if "portions" in needs else 0
         if "latent_attention" in needs:
             # The latent attention takes 64 (row, head) pairs of one portion per block: rows x heads / 64 blocks and at
             # most one more per portion. A step of single tokens may be replayed as a captured graph with other
@@ -291,7 +294,7 @@ class CudaOps(Ops):
     def step_signature(self, meta) -> tuple:
         """What, beside the row counts, fixes the kernel launches of a step (two steps that agree in it launch alike)."""
         plan = meta.plan
-        latent = (getattr(meta, "latent_extra", 0),)
+        latent = (getattr(meta, "latent_extra", 0), getattr(meta, "portion_tiles", 0))
         return (plan.n_tiles, plan.n_short_rows > 0, plan.n_cuts, plan.single_tokens, *latent) if plan is not None else latent
 
     def check_attention(self, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
@@ -966,11 +969,27 @@ class CudaOps(Ops):
         if self._profile is not None:
             seen = sum(min(sg.pos0 + i + 1, (window + keep_first) if window else sg.pos0 + i + 1) for sg in meta.segments for i in range(sg.n))
             nbytes = seen * num_kv_heads * (key_dim + value_dim) * k.element_size() + n * num_heads * (key_dim + value_dim) * q.element_size()
+        # A step of single tokens (bfloat16): a row's keys are cut into runs of chunks, one block each, and merged by a
+        # second kernel, so that a few rows fill the GPU. Other steps: blocks of consecutive rows of a portion that share
+        # their key and value loads. (float32 keeps the one arithmetic for every step: a position's bits do not depend
+        # on the cutting.)
+        max_portion = max(1, int(getattr(meta, "max_portion", 0)) or n)
+        unit_chunks = units = 0
+        part = None
+        if self.split_decode_keys and self.dtype == torch.bfloat16 and max_portion == 1:
+            ctx = max(1, int(meta.max_context))
+            unit_chunks = 2 if window else max(2, -(-ctx // (32 * 64)))
+            units = int(self.seq.fz_sink_attention_units(c_int(window), c_int(keep_first), c_int(ctx), c_int(unit_chunks)))
+            part = self._scratch("sink attention partials", n * num_heads * units * (value_dim + 2), torch.float32)
         self._check(self.seq.fz_sink_attention(
-            _p(q), _p(k), _p(v), _p(meta.pos), _p(meta.seq_row), _p(table), c_int(table.shape[1]), c_longlong(k.stride(0)),
+            _p(q), _p(k), _p(v), _p(meta.pos), _p(meta.seq_row), _p(meta.seg), c_int(getattr(meta, "max_segments", meta.n_segments)),
+            c_int(max_portion), _p(table), c_int(table.shape[1]), c_longlong(k.stride(0)),
             c_longlong(k.stride(1)), c_longlong(k.stride(2)), c_int(cache.page_size), c_int(k.shape[0]), _p(out),
             c_int(_CODE[self.dtype]), c_int(n), c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim),
-            c_float(scale), c_int(window), c_int(keep_first), _p(sink), _p(self.err), self._stream()), "sink_attention", nbytes)
+            c_float(scale), c_int(window), c_int(keep_first), _p(sink), c_int(unit_chunks), c_int(units), _p(part),
+            _p(self.err), self._stream()), "sink_attention", nbytes)
+        if units:
+            self.launches += 1      # the merge kernel
 
     def weighted_sum(self, terms, weights, out) -> None:
         if not 1 <= len(terms) <= 4 or len(weights) != len(terms):

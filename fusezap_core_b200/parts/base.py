@@ -88,7 +88,8 @@ class Part:
     def step_needs(self) -> tuple[str, ...]:
         """Kinds of per-step data this part's kernels need beside the common metadata: "attention" (the kernel table
         plans its attention kernels' tiles for every step), "token_ids" (the step's token ids as one device tensor,
-        `ctx.token_ids`, also where a token comes from the ids the previous step left on the device). None by default."""
+        `ctx.token_ids`, also where a token comes from the ids the previous step left on the device), "portions" (its
+        kernels size their launches by the step's longest portion, which is then part of a step's shape). None by default."""
         return ()
 
     def weight_tensors(self) -> list[torch.Tensor]:

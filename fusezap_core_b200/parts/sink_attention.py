@@ -61,6 +61,9 @@ class SinkAttention(Mixer):
     def position_name(self) -> str | None:
         return self.position
 
+    def step_needs(self) -> tuple[str, ...]:
+        return ("portions",)      # its kernels tile the rows of portions: the longest portion is part of a step's shape
+
     def forward(self, ctx, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         n, ops, ws = h.shape[0], ctx.ops, ctx.ws
         Hq, Hkv, dk, dv = self.Hq, self.Hkv, self.dk, self.dv
