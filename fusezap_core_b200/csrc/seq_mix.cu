@@ -196,7 +196,7 @@ sink_attention_tile_kernel(const AttnArgs a) {
   fz_grid_wait();
   const int r0 = blockIdx.y * a.rows_per_block;
   if (r0 >= cnt) return;
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int G_all = a.Hq / a.Hkv, slices = (G_all + MAX_PAIRS - 1) / MAX_PAIRS;
   const int kvh = blockIdx.z / slices, g_base = (blockIdx.z % slices) * MAX_PAIRS;
   const int G = min(MAX_PAIRS, G_all - g_base);
@@ -260,7 +260,7 @@ sink_attention_unit_kernel(const AttnArgs a) {
   const ChunkWalk walk(p, p, a.window, a.keep_first);
   const int it0 = blockIdx.z * a.unit_chunks;
   if (it0 >= walk.count) return;
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int G_all = a.Hq / a.Hkv, slices = (G_all + MAX_PAIRS - 1) / MAX_PAIRS;
   const int kvh = blockIdx.y / slices, g_base = (blockIdx.y % slices) * MAX_PAIRS;
   const int G = min(MAX_PAIRS, G_all - g_base);
@@ -344,48 +344,74 @@ sink_attention_merge_kernel(const AttnArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------------ recurrent scans
-// The state of a head is a key_dim x value_dim matrix S. A thread owns DPT = 16 consecutive rows of DC = 4 neighbouring
-// columns (64 values in registers: every key and query value it reads from shared memory serves four columns, and the
-// 64 independent chains hide the latencies of the token-by-token recurrence); the R lanes that share the columns (R a
-// power of two, R * 16 >= key_dim; lane = r * (32 / R) + group, so that the lanes of a quarter warp read one address)
-// add their partial dot products with shuffles. State layout in memory: (slots, heads, value_dim, R * 16), so a thread's 16 values are contiguous and a
-// column's run is read in 64-byte pieces; rows beyond key_dim stay zero. A block covers (blockDim / R) * 4 columns of one
+// The state of a head is a key_dim x value_dim matrix S. A thread owns DPT = 8 consecutive rows of DC = 4 neighbouring
+// columns, as sixteen packed pairs: the recurrence runs on packed float32 x 2 instructions (each half rounds as the scalar
+// instruction does), every key and query value read from shared memory serves four columns, and a head is spread over
+// value_dim / 4 x R threads (the kernels are bound by the instructions they issue per token, not by memory). The R lanes that share the columns (R a power of two, R * 8 >= key_dim; lane = r * (32 / R)
+// + group, so that neighbouring lanes read one address of shared memory) add their partial dot products with shuffles.
+// State layout in memory: (slots, heads, value_dim, R * 8), so a thread's 8 values of a column are contiguous and a
+// column's run is read in 32-byte pieces; rows beyond key_dim stay zero. A block covers (blockDim / R) * 4 columns of one
 // head of one portion and walks the portion's tokens in chunks, staged in shared memory by all threads.
-constexpr int DPT = 16;
-constexpr int DC = 4;                       // value columns per thread
-constexpr int SCAN_MAX_THREADS = 256;
+constexpr int DPT = 8;
+constexpr int DC = 4;                       // value columns per thread: two packed pairs
+constexpr int SCAN_MAX_THREADS = 512;
 // While a chunk of tokens is computed, the inputs of the next one travel from global into a raw staging area of shared
 // memory (`cp.async`, four bytes each); after the chunk they are turned into what the recurrence reads (rotated or unit
 // vectors, decays, gates) in a second area. tch: tokens per chunk (16, or 8 where shared memory would not hold 16).
 
 // Sum over the R lanes that hold the rows of one column group: they are 32 / R lanes apart.
-__device__ __forceinline__ float lanes_sum(float v, int R) {
+template <int R>
+__device__ __forceinline__ float lanes_sum(float v) {
+#pragma unroll
   for (int o = 16; o >= 32 / R; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
 
 // Which column group (of the block) and which 16 rows a thread owns.
-__device__ __forceinline__ void scan_place(int R, int& group, int& r) {
-  const int per_warp = 32 / R, lane = threadIdx.x & 31;
+template <int R>
+__device__ __forceinline__ void scan_place(int& group, int& r) {
+  constexpr int per_warp = 32 / R;
+  const int lane = threadIdx.x & 31;
   r = lane / per_warp;
   group = (threadIdx.x >> 5) * per_warp + lane % per_warp;
 }
 
-__device__ __forceinline__ void load_state(const float* __restrict__ p, float* S) {
+// The thread's 8 rows of two neighbouring columns (dkp floats apart), as pairs (column, column + 1); the second column
+// is read and written only where it exists.
+__device__ __forceinline__ void load_state(const float* __restrict__ p, int dkp, bool first, bool second, float2* S) {
 #pragma unroll
   for (int i = 0; i < DPT; i += 4) {
-    const float4 v = *(const float4*)(p + i);
-    S[i] = v.x; S[i + 1] = v.y; S[i + 2] = v.z; S[i + 3] = v.w;
+    const float4 a = first ? *(const float4*)(p + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 b = second ? *(const float4*)(p + dkp + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    S[i] = make_float2(a.x, b.x); S[i + 1] = make_float2(a.y, b.y); S[i + 2] = make_float2(a.z, b.z); S[i + 3] = make_float2(a.w, b.w);
   }
 }
-__device__ __forceinline__ void store_state(float* __restrict__ p, const float* S) {
+__device__ __forceinline__ void store_state(float* __restrict__ p, int dkp, bool first, bool second, const float2* S) {
 #pragma unroll
-  for (int i = 0; i < DPT; i += 4) *(float4*)(p + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+  for (int i = 0; i < DPT; i += 4) {
+    if (first) *(float4*)(p + i) = make_float4(S[i].x, S[i + 1].x, S[i + 2].x, S[i + 3].x);
+    if (second) *(float4*)(p + dkp + i) = make_float4(S[i].y, S[i + 1].y, S[i + 2].y, S[i + 3].y);
+  }
 }
+__device__ __forceinline__ void load8(const float* p, float* v) {       // 8 floats from shared memory, 32-byte aligned
+  const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ float2 both(float v) { return make_float2(v, v); }
 
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+// Unit i of `vec` four-byte words (1 or 4) from src to dst.
+__device__ __forceinline__ void cp_words(float* dst, const float* src, int i, int vec) {
+  if (vec == 4) cp_async16(dst + 4 * i, src + 4 * i);
+  else cp_async4(dst + i, src + i);
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
@@ -400,8 +426,9 @@ __device__ __forceinline__ void stage_unit(T* dst, const T* src, int i, bool wor
 }
 
 // S = decay * S + k' v^T; o = S^T q'. proj rows: [q heads | k heads | v heads | ...], ld floats apart.
+template <int R>
 __global__ void __launch_bounds__(SCAN_MAX_THREADS)
-retention_scan_kernel(const float* __restrict__ proj, int ld, int H, int dk, int dv, int R, int tch,
+retention_scan_kernel(const float* __restrict__ proj, int ld, int H, int dk, int dv, int tch,
                       const float* __restrict__ decay, float key_scale, const float* __restrict__ cos_t,
                       const float* __restrict__ sin_t, int rotated, int pairing, int max_pos, float* __restrict__ state,
                       const int* __restrict__ seg, float* __restrict__ out, int* err) {
@@ -411,7 +438,7 @@ retention_scan_kernel(const float* __restrict__ proj, int ld, int H, int dk, int
   fz_grid_wait();
   if (cnt <= 0 || slot < 0) return;
   if (rotated > 0 && (pos0 < 0 || pos0 + cnt > max_pos)) { if (threadIdx.x == 0) atomicOr(err, FZ_ERR_POS_RANGE); return; }
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int NT = blockDim.x;
   const int dkp = R * DPT, COLS = NT / R * DC, half = rotated >> 1;
   float* qs = smem;                    // [tch][dkp]   what the recurrence reads
@@ -423,35 +450,34 @@ retention_scan_kernel(const float* __restrict__ proj, int ld, int H, int dk, int
   float* rc = rv + tch * COLS;         // [tch][half]  the rows of the cosine and sine tables
   float* rs = rc + tch * half;         // [tch][half]
   int group, r;
-  scan_place(R, group, r);
+  scan_place<R>(group, r);
   const int col0 = blockIdx.z * COLS, col = col0 + group * DC;      // this thread's first column
   const int ncols = min(COLS, dv - col0);
   float* sp = state + (((size_t)slot * H + h) * dv + col) * dkp + r * DPT;
-  float S[DC][DPT];
-#pragma unroll
-  for (int j = 0; j < DC; ++j) {
-    if (col + j < dv) load_state(sp + (size_t)j * dkp, S[j]);
-    else {
-#pragma unroll
-      for (int i = 0; i < DPT; ++i) S[j][i] = 0.f;
-    }
-  }
-  const float dec = decay[h];
-  const int per_token = 2 * dk + ncols + 2 * half;      // values a token brings: q, k, its columns of v, cosines, sines
+  const bool has[DC] = {col < dv, col + 1 < dv, col + 2 < dv, col + 3 < dv};
+  float2 S[DC / 2][DPT];
+  load_state(sp, dkp, has[0], has[1], S[0]);
+  load_state(sp + 2 * (size_t)dkp, dkp, has[2], has[3], S[1]);
+  const float2 dec = both(decay[h]);
+  // what a token brings: q, k, its columns of v, cosines, sines; in copies of 16 bytes where every run starts on a 16-byte
+  // boundary and has a length that is a multiple of four, else of 4 bytes
+  const int vec = ((dk | ld | dv | ncols | half) & 3) == 0 && aligned16(proj) && (half == 0 || (aligned16(cos_t) && aligned16(sin_t))) ? 4 : 1;
+  const int uq = dk / vec, uv = ncols / vec, uh = half / vec;
+  const int per_token = 2 * uq + uv + 2 * uh;
   auto issue = [&](int t0) {
     const int tc = min(tch, cnt - t0);
     for (int e = threadIdx.x; e < tc * per_token; e += NT) {
       const int tt = e / per_token;
       int i = e - tt * per_token;
       const float* in = proj + (size_t)(row0 + t0 + tt) * ld;
-      if (i < dk) { cp_async4(rq + tt * dk + i, in + (size_t)h * dk + i); continue; }
-      i -= dk;
-      if (i < dk) { cp_async4(rk + tt * dk + i, in + (size_t)(H + h) * dk + i); continue; }
-      i -= dk;
-      if (i < ncols) { cp_async4(rv + tt * COLS + i, in + (size_t)2 * H * dk + (size_t)h * dv + col0 + i); continue; }
-      i -= ncols;
-      if (i < half) cp_async4(rc + tt * half + i, cos_t + (size_t)(pos0 + t0 + tt) * half + i);
-      else cp_async4(rs + tt * half + i - half, sin_t + (size_t)(pos0 + t0 + tt) * half + i - half);
+      if (i < uq) { cp_words(rq + tt * dk, in + (size_t)h * dk, i, vec); continue; }
+      i -= uq;
+      if (i < uq) { cp_words(rk + tt * dk, in + (size_t)(H + h) * dk, i, vec); continue; }
+      i -= uq;
+      if (i < uv) { cp_words(rv + tt * COLS, in + (size_t)2 * H * dk + (size_t)h * dv + col0, i, vec); continue; }
+      i -= uv;
+      if (i < uh) cp_words(rc + tt * half, cos_t + (size_t)(pos0 + t0 + tt) * half, i, vec);
+      else cp_words(rs + tt * half, sin_t + (size_t)(pos0 + t0 + tt) * half, i - uh, vec);
     }
     cp_async_commit();
   };
@@ -482,28 +508,29 @@ retention_scan_kernel(const float* __restrict__ proj, int ld, int H, int dk, int
     const int tc = min(tch, cnt - t0);
     const bool more = t0 + tch < cnt;
     if (more) issue(t0 + tch);
-    for (int tt = 0; tt < tc; ++tt) {
+    float* dst = out + (size_t)(row0 + t0) * H * dv + (size_t)h * dv + col;
+#pragma unroll 2
+    for (int tt = 0; tt < tc; ++tt, dst += (size_t)H * dv) {
       const float4 v4 = *(const float4*)(vs + tt * COLS + group * DC);
-      const float v[DC] = {v4.x, v4.y, v4.z, v4.w};
-      const float* kk = ks + tt * dkp + r * DPT;
-      const float* qq = qs + tt * dkp + r * DPT;
-      float o[DC] = {0.f, 0.f, 0.f, 0.f};
+      const float2 v[DC / 2] = {make_float2(v4.x, v4.y), make_float2(v4.z, v4.w)};
+      float kk[DPT], qq[DPT];
+      load8(ks + tt * dkp + r * DPT, kk);
+      load8(qs + tt * dkp + r * DPT, qq);
+      float2 o[DC / 2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {
-        const float ki = kk[i], qi = qq[i];
+        const float2 k2 = both(kk[i]), q2 = both(qq[i]);
 #pragma unroll
-        for (int j = 0; j < DC; ++j) {
-          S[j][i] = __fmaf_rn(dec, S[j][i], __fmul_rn(ki, v[j]));
-          o[j] = __fmaf_rn(S[j][i], qi, o[j]);
+        for (int j = 0; j < DC / 2; ++j) {
+          S[j][i] = __ffma2_rn(dec, S[j][i], __fmul2_rn(k2, v[j]));
+          o[j] = __ffma2_rn(S[j][i], q2, o[j]);
         }
       }
-#pragma unroll
-      for (int j = 0; j < DC; ++j) o[j] = lanes_sum(o[j], R);
+      const float res[DC] = {lanes_sum<R>(o[0].x), lanes_sum<R>(o[0].y), lanes_sum<R>(o[1].x), lanes_sum<R>(o[1].y)};
       if (r == 0) {
-        float* dst = out + (size_t)(row0 + t0 + tt) * H * dv + (size_t)h * dv + col;
 #pragma unroll
         for (int j = 0; j < DC; ++j)
-          if (col + j < dv) dst[j] = o[j];
+          if (has[j]) dst[j] = res[j];
       }
     }
     if (more) {
@@ -513,15 +540,14 @@ retention_scan_kernel(const float* __restrict__ proj, int ld, int H, int dk, int
       __syncthreads();
     }
   }
-#pragma unroll
-  for (int j = 0; j < DC; ++j)
-    if (col + j < dv) store_state(sp + (size_t)j * dkp, S[j]);
+  store_state(sp, dkp, has[0], has[1], S[0]);
+  store_state(sp + 2 * (size_t)dkp, dkp, has[2], has[3], S[1]);
 }
 
 // S = g * S (rows); u = beta (v - S^T k^); S += k^ u^T; o = S^T q^. qkv rows: [q (Hk dk) | k (Hk dk) | v (H dv)] of T.
-template <typename T>
+template <typename T, int R>
 __global__ void __launch_bounds__(SCAN_MAX_THREADS)
-gated_delta_scan_kernel(const T* __restrict__ qkv, int H, int Hk, int dk, int dv, int R, int tch,
+gated_delta_scan_kernel(const T* __restrict__ qkv, int H, int Hk, int dk, int dv, int tch,
                         const float* __restrict__ high, int ldh, const float* __restrict__ beta,
                         const float* __restrict__ a_log, const float* __restrict__ dt_bias, float unit_eps, float q_scale,
                         float* __restrict__ state, const int* __restrict__ seg, float* __restrict__ out) {
@@ -530,7 +556,7 @@ gated_delta_scan_kernel(const T* __restrict__ qkv, int H, int Hk, int dk, int dv
   const int row0 = seg[4 * s], cnt = seg[4 * s + 1], slot = seg[4 * s + 3];
   fz_grid_wait();
   if (cnt <= 0 || slot < 0) return;
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int NT = blockDim.x;
   const int dkp = R * DPT, COLS = NT / R * DC;
   const int dke = (dk + 1) & ~1, cole = (COLS + 1) & ~1;      // raw rows of T start on four-byte boundaries
@@ -545,7 +571,7 @@ gated_delta_scan_kernel(const T* __restrict__ qkv, int H, int Hk, int dk, int dv
   T* rk = rq + tch * dke;
   T* rv = rk + tch * dke;              // [tch][cole]
   int group, r;
-  scan_place(R, group, r);
+  scan_place<R>(group, r);
   const int col0 = blockIdx.z * COLS, col = col0 + group * DC;      // this thread's first column
   const int ncols = min(COLS, dv - col0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -554,19 +580,16 @@ gated_delta_scan_kernel(const T* __restrict__ qkv, int H, int Hk, int dk, int dv
   // 16-bit values travel in pairs where every run starts on a four-byte boundary and has an even length
   const bool words = sizeof(T) == 4 || (((dk | dv | C | col0 | ncols) & 1) == 0 && ((uintptr_t)qkv & 3) == 0);
   float* sp = state + (((size_t)slot * H + h) * dv + col) * dkp + r * DPT;
-  float S[DC][DPT];
-#pragma unroll
-  for (int j = 0; j < DC; ++j) {
-    if (col + j < dv) load_state(sp + (size_t)j * dkp, S[j]);
-    else {
-#pragma unroll
-      for (int i = 0; i < DPT; ++i) S[j][i] = 0.f;
-    }
-  }
+  const bool has[DC] = {col < dv, col + 1 < dv, col + 2 < dv, col + 3 < dv};
+  float2 S[DC / 2][DPT];
+  load_state(sp, dkp, has[0], has[1], S[0]);
+  load_state(sp + 2 * (size_t)dkp, dkp, has[2], has[3], S[1]);
   const float rate = expf(a_log[h]);
   const bool pairs = sizeof(T) == 2 && words;
   const int uq = pairs ? dk / 2 : dk, uv = pairs ? ncols / 2 : ncols;      // copies per run of q or k, and of v
-  const int per_token = 2 * uq + uv + dk + 1;
+  const int avec = ((dk | ldh) & 3) == 0 && aligned16(high) ? 4 : 1;      // the float32 decay inputs: 16 bytes a copy where aligned
+  const int ua = dk / avec;
+  const int per_token = 2 * uq + uv + ua + 1;
   auto issue = [&](int t0) {
     const int tc = min(tch, cnt - t0);
     for (int e = threadIdx.x; e < tc * per_token; e += NT) {
@@ -580,7 +603,7 @@ gated_delta_scan_kernel(const T* __restrict__ qkv, int H, int Hk, int dk, int dv
       i -= uq;
       if (i < uv) { stage_unit(rv + tt * cole, in + (size_t)2 * Hk * dk + (size_t)h * dv + col0, i, words); continue; }
       i -= uv;
-      if (i < dk) cp_async4(ra + tt * dk + i, high + n * ldh + (size_t)h * dk + i);
+      if (i < ua) cp_words(ra + tt * dk, high + n * ldh + (size_t)h * dk, i, avec);
       else cp_async4(rb + tt, beta + n * H + h);
     }
     cp_async_commit();
@@ -627,42 +650,42 @@ gated_delta_scan_kernel(const T* __restrict__ qkv, int H, int Hk, int dk, int dv
     const int tc = min(tch, cnt - t0);
     const bool more = t0 + tch < cnt;
     if (more) issue(t0 + tch);
-    for (int tt = 0; tt < tc; ++tt) {
+    float* dst = out + (size_t)(row0 + t0) * H * dv + (size_t)h * dv + col;
+#pragma unroll 2
+    for (int tt = 0; tt < tc; ++tt, dst += (size_t)H * dv) {
       const float4 v4 = *(const float4*)(vs + tt * COLS + group * DC);
-      const float v[DC] = {v4.x, v4.y, v4.z, v4.w};
       const float b = bs[tt];
-      const float* kk = ks + tt * dkp + r * DPT;
-      const float* qq = qs + tt * dkp + r * DPT;
-      const float* gg = gs + tt * dkp + r * DPT;
-      float ksum[DC] = {0.f, 0.f, 0.f, 0.f};
+      float kk[DPT], qq[DPT], gg[DPT];
+      load8(ks + tt * dkp + r * DPT, kk);
+      load8(qs + tt * dkp + r * DPT, qq);
+      load8(gs + tt * dkp + r * DPT, gg);
+      float2 ksum[DC / 2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {
-        const float gi = gg[i], ki = kk[i];
+        const float2 g2 = both(gg[i]), k2 = both(kk[i]);
 #pragma unroll
-        for (int j = 0; j < DC; ++j) {
-          S[j][i] = __fmul_rn(gi, S[j][i]);
-          ksum[j] = __fmaf_rn(S[j][i], ki, ksum[j]);
+        for (int j = 0; j < DC / 2; ++j) {
+          S[j][i] = __fmul2_rn(g2, S[j][i]);
+          ksum[j] = __ffma2_rn(S[j][i], k2, ksum[j]);
         }
       }
-      float u[DC], o[DC] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int j = 0; j < DC; ++j) u[j] = __fmul_rn(b, v[j] - lanes_sum(ksum[j], R));
+      const float2 u[DC / 2] = {make_float2(__fmul_rn(b, v4.x - lanes_sum<R>(ksum[0].x)), __fmul_rn(b, v4.y - lanes_sum<R>(ksum[0].y))),
+                                make_float2(__fmul_rn(b, v4.z - lanes_sum<R>(ksum[1].x)), __fmul_rn(b, v4.w - lanes_sum<R>(ksum[1].y)))};
+      float2 o[DC / 2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {
-        const float ki = kk[i], qi = qq[i];
+        const float2 k2 = both(kk[i]), q2 = both(qq[i]);
 #pragma unroll
-        for (int j = 0; j < DC; ++j) {
-          S[j][i] = __fmaf_rn(ki, u[j], S[j][i]);
-          o[j] = __fmaf_rn(S[j][i], qi, o[j]);
+        for (int j = 0; j < DC / 2; ++j) {
+          S[j][i] = __ffma2_rn(k2, u[j], S[j][i]);
+          o[j] = __ffma2_rn(S[j][i], q2, o[j]);
         }
       }
-#pragma unroll
-      for (int j = 0; j < DC; ++j) o[j] = lanes_sum(o[j], R);
+      const float res[DC] = {lanes_sum<R>(o[0].x), lanes_sum<R>(o[0].y), lanes_sum<R>(o[1].x), lanes_sum<R>(o[1].y)};
       if (r == 0) {
-        float* dst = out + (size_t)(row0 + t0 + tt) * H * dv + (size_t)h * dv + col;
 #pragma unroll
         for (int j = 0; j < DC; ++j)
-          if (col + j < dv) dst[j] = o[j];
+          if (has[j]) dst[j] = res[j];
       }
     }
     if (more) {
@@ -672,9 +695,8 @@ gated_delta_scan_kernel(const T* __restrict__ qkv, int H, int Hk, int dk, int dv
       __syncthreads();
     }
   }
-#pragma unroll
-  for (int j = 0; j < DC; ++j)
-    if (col + j < dv) store_state(sp + (size_t)j * dkp, S[j]);
+  store_state(sp, dkp, has[0], has[1], S[0]);
+  store_state(sp + 2 * (size_t)dkp, dkp, has[2], has[3], S[1]);
 }
 
 // out[n, h, c] = o / sqrt(mean_c o^2 + eps) * w[c] * act(gate[n, goff + h dv + c]); a warp per (row, head).
@@ -720,7 +742,7 @@ router_topk_kernel(const float* __restrict__ logits, int ld, int N, int E, int t
                    const int* __restrict__ seq_row, int* __restrict__ choice, float* __restrict__ weight) {
   fz_grid_launch_dependents();
   fz_grid_wait();
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * ROUTER_WARPS + warp;
   if (n >= N) return;
@@ -932,9 +954,9 @@ FZ_API int fz_sink_attention(const void* q, const void* k_pool, const void* v_po
   return FZ_BAD_DTYPE;
 }
 
-// The padded key size of the recurrent state, (slots, heads, value_dim, this): 16 times a power of two, at most 512.
+// The padded key size of the recurrent state, (slots, heads, value_dim, this): 8 times a power of two, at most 256.
 FZ_API int fz_recurrent_key_pad(int dk) {
-  if (dk <= 0 || dk > 512) return -1;
+  if (dk <= 0 || dk > 32 * DPT) return -1;
   return lanes_per_column(dk) * DPT;
 }
 
@@ -953,35 +975,54 @@ static size_t delta_smem(int dk, int R, int cols, int tch, size_t elem) {
   return sizeof(float) * (size_t)tch * ((size_t)3 * dkp + cols + 1 + dk + 1) + elem * (size_t)tch * (2 * ((dk + 1) & ~1) + ((cols + 1) & ~1)) + 16;
 }
 
+template <int R>
+static int launch_retention(const float* proj, int ld, int H, int dk, int dv, const float* decay, float key_scale,
+                            const float* cos_t, const float* sin_t, int rotated, int pairing, int max_pos, float* state,
+                            const int* seg, int n_seg, float* out, int* err, cudaStream_t stream) {
+  const int threads = scan_threads(dv, R), cols = threads / R * DC;
+  const int tch = retention_smem(dk, R, cols, rotated, 16) <= 48 * 1024 ? 16 : 8;
+  const size_t smem = retention_smem(dk, R, cols, rotated, tch);
+  static size_t allowed = 48 * 1024;
+  int st = allow_smem(retention_scan_kernel<R>, smem, allowed);
+  if (st != FZ_OK) return st;
+  fz_launch(retention_scan_kernel<R>, dim3(n_seg, H, (dv + cols - 1) / cols), dim3(threads), smem, stream, proj, ld, H, dk, dv,
+            tch, decay, key_scale, cos_t, sin_t, rotated, pairing, max_pos, state, seg, out, err);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+#define FZ_BY_LANES(R, CALL)          \
+  switch (R) {                        \
+    case 1: return CALL(1);           \
+    case 2: return CALL(2);           \
+    case 4: return CALL(4);           \
+    case 8: return CALL(8);           \
+    case 16: return CALL(16);         \
+    default: return CALL(32);         \
+  }
+
 FZ_API int fz_retention_scan(const float* proj, int ld, int H, int dk, int dv, const float* decay, float key_scale,
                              const float* cos_t, const float* sin_t, int rotated, int pairing, int max_pos, float* state,
                              const int* seg, int n_seg, float* out, int* err, cudaStream_t stream) {
   if (n_seg <= 0) return FZ_OK;
   if (H <= 0 || H > 65535 || dv <= 0 || fz_recurrent_key_pad(dk) < 0 || rotated < 0 || rotated > dk || (rotated & 1)) return FZ_BAD_SHAPE;
-  const int R = lanes_per_column(dk), threads = scan_threads(dv, R), cols = threads / R * DC;
-  const int tch = retention_smem(dk, R, cols, rotated, 16) <= 48 * 1024 ? 16 : 8;
-  const size_t smem = retention_smem(dk, R, cols, rotated, tch);
-  static size_t allowed = 48 * 1024;
-  int st = allow_smem(retention_scan_kernel, smem, allowed);
-  if (st != FZ_OK) return st;
-  fz_launch(retention_scan_kernel, dim3(n_seg, H, (dv + cols - 1) / cols), dim3(threads), smem, stream, proj, ld, H, dk, dv,
-            R, tch, decay, key_scale, cos_t, sin_t, rotated, pairing, max_pos, state, seg, out, err);
-  FZ_LAUNCH_CHECK();
-  return FZ_OK;
+#define FZ_CALL(R) launch_retention<R>(proj, ld, H, dk, dv, decay, key_scale, cos_t, sin_t, rotated, pairing, max_pos, state, seg, n_seg, out, err, stream)
+  FZ_BY_LANES(lanes_per_column(dk), FZ_CALL)
+#undef FZ_CALL
 }
 
-template <typename T>
+template <typename T, int R>
 static int launch_delta(const void* qkv, int H, int Hk, int dk, int dv, const float* high, int ldh, const float* beta,
                         const float* a_log, const float* dt_bias, float unit_eps, float q_scale, float* state, const int* seg,
                         int n_seg, float* out, cudaStream_t stream) {
-  const int R = lanes_per_column(dk), threads = scan_threads(dv, R), cols = threads / R * DC;
+  const int threads = scan_threads(dv, R), cols = threads / R * DC;
   const int tch = delta_smem(dk, R, cols, 16, sizeof(T)) <= 48 * 1024 ? 16 : 8;
   const size_t smem = delta_smem(dk, R, cols, tch, sizeof(T));
   static size_t allowed = 48 * 1024;
-  int st = allow_smem(gated_delta_scan_kernel<T>, smem, allowed);
+  int st = allow_smem(gated_delta_scan_kernel<T, R>, smem, allowed);
   if (st != FZ_OK) return st;
-  fz_launch(gated_delta_scan_kernel<T>, dim3(n_seg, H, (dv + cols - 1) / cols), dim3(threads), smem, stream, (const T*)qkv,
-            H, Hk, dk, dv, R, tch, high, ldh, beta, a_log, dt_bias, unit_eps, q_scale, state, seg, out);
+  fz_launch(gated_delta_scan_kernel<T, R>, dim3(n_seg, H, (dv + cols - 1) / cols), dim3(threads), smem, stream, (const T*)qkv,
+            H, Hk, dk, dv, tch, high, ldh, beta, a_log, dt_bias, unit_eps, q_scale, state, seg, out);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }
@@ -991,10 +1032,12 @@ FZ_API int fz_gated_delta_scan(const void* qkv, int dtype, int H, int Hk, int dk
                                float* state, const int* seg, int n_seg, float* out, cudaStream_t stream) {
   if (n_seg <= 0) return FZ_OK;
   if (H <= 0 || H > 65535 || Hk <= 0 || H % Hk || dv <= 0 || fz_recurrent_key_pad(dk) < 0) return FZ_BAD_SHAPE;
-  if (dtype == FZ_F32)
-    return launch_delta<float>(qkv, H, Hk, dk, dv, high, ldh, beta, a_log, dt_bias, unit_eps, q_scale, state, seg, n_seg, out, stream);
-  if (dtype == FZ_BF16)
-    return launch_delta<__nv_bfloat16>(qkv, H, Hk, dk, dv, high, ldh, beta, a_log, dt_bias, unit_eps, q_scale, state, seg, n_seg, out, stream);
+#define FZ_CALL_F(R) launch_delta<float, R>(qkv, H, Hk, dk, dv, high, ldh, beta, a_log, dt_bias, unit_eps, q_scale, state, seg, n_seg, out, stream)
+#define FZ_CALL_B(R) launch_delta<__nv_bfloat16, R>(qkv, H, Hk, dk, dv, high, ldh, beta, a_log, dt_bias, unit_eps, q_scale, state, seg, n_seg, out, stream)
+  if (dtype == FZ_F32) { FZ_BY_LANES(lanes_per_column(dk), FZ_CALL_F) }
+  if (dtype == FZ_BF16) { FZ_BY_LANES(lanes_per_column(dk), FZ_CALL_B) }
+#undef FZ_CALL_F
+#undef FZ_CALL_B
   return FZ_BAD_DTYPE;
 }
 

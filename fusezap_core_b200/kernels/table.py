@@ -827,10 +827,10 @@ class CudaOps(Ops):
 
     # ---- recurrent mixers, attention with a window, kept first tokens and a sink, routed experts
     def recurrent_state_shape(self, heads: int, key_dim: int, value_dim: int) -> tuple:
-        """(heads, value_dim, padded key_dim): a column of S is contiguous, padded to 16 times a power of two."""
+        """(heads, value_dim, padded key_dim): a column of S is contiguous, padded to 8 times a power of two."""
         pad = int(self.seq.fz_recurrent_key_pad(c_int(key_dim)))
         if pad < 0:
-            raise ValueError(f"a recurrent state with {key_dim} key dimensions is not supported (1..512)")
+            raise ValueError(f"a recurrent state with {key_dim} key dimensions is not supported (1..256)")
         return (heads, value_dim, pad)
 
     def _state(self, state, heads, key_dim, value_dim, what):
