@@ -272,7 +272,8 @@ def scan_portions(total, seed):
     return steps
 
 
-@pytest.mark.parametrize("H,dk,dv,rotated,pairing", [(2, 16, 24, 8, 0), (3, 40, 8, 40, 1), (1, 128, 64, 64, 0), (2, 24, 100, 0, 0), (5, 8, 300, 8, 1)])
+@pytest.mark.parametrize("H,dk,dv,rotated,pairing", [(2, 16, 24, 8, 0), (3, 40, 8, 40, 1), (1, 128, 64, 64, 0), (2, 24, 100, 0, 0), (5, 8, 300, 8, 1),
+                                                     (2, 9, 7, 4, 1), (1, 200, 6, 100, 0)])
 def test_retention_scan_carries_its_state_across_portions(H, dk, dv, rotated, pairing):
     ops, g, T = cuda_ops("float32"), torch.Generator().manual_seed(dk), 70
     rot = {"base": 50.0, "dims": rotated}
@@ -305,7 +306,8 @@ def test_retention_scan_carries_its_state_across_portions(H, dk, dv, rotated, pa
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,Hk,dk,dv", [(4, 2, 8, 16), (2, 1, 20, 12), (1, 1, 16, 32), (3, 3, 12, 8), (2, 2, 128, 40), (6, 3, 48, 260)])
+@pytest.mark.parametrize("H,Hk,dk,dv", [(4, 2, 8, 16), (2, 1, 20, 12), (1, 1, 16, 32), (3, 3, 12, 8), (2, 2, 128, 40), (6, 3, 48, 260),
+                                        (2, 1, 9, 7), (1, 1, 136, 10)])
 def test_gated_delta_scan_carries_its_state_across_portions(dtype, H, Hk, dk, dv):
     ops, g, T, dt = cuda_ops(dtype), torch.Generator().manual_seed(dk + dv), 60, DT[dtype]
     C = 2 * Hk * dk + H * dv
