@@ -24,6 +24,7 @@ _DEVICE_ERRORS = {1: "a token id lies outside the embedding table", 2: "a positi
                   16: "a selected row lies outside the step"}
 
 
+SINK_MMA_ROWS = 16  # windowed attention with a sink: steps whose longest portion has this many rows go to the tensor-core kernel
 LONG_PORTION = 8    # attention: portions of at least this many tokens go to the tile (prefill) kernels
 TILE_ROWS = 128     # token rows per tile of those kernels
 
@@ -120,7 +121,7 @@ class CudaOps(Ops):
         if self.dtype == torch.bfloat16:
             self.tc = load("fzb200_tc")      # tcgen05 / TMA kernels
         self.use_tensor_cores = self.tc is not None
-        self._attn_tc = self._mix = self._mix_tc = self._latent = self._latent_tc = self._seq = None   # libraries loaded (and built) when a part first asks for their kernels
+        self._attn_tc = self._mix = self._mix_tc = self._latent = self._latent_tc = self._seq = self._seq_tc = None   # libraries loaded (and built) when a part first asks for their kernels
         self.prefill_tcgen05 = True        # False: long portions on the mma.sync flash-attention kernel
         self.fuse_swiglu = True            # gate/up product and SwiGLU in one kernel where the sizes allow it
         self.fuse_argmax = True            # lm_head product and argmax in one pass where no logits are asked for
@@ -135,6 +136,7 @@ class CudaOps(Ops):
         self._profile = None               # a StepProfile while the engine profiles its steps
         self._meta_rows = None             # meta.seq_row of the step being run, for ops that take no `meta`
         self.split_decode_keys = True      # windowed attention with a sink: steps of single tokens cut a row's keys into runs
+        self.sink_tensor_cores = True      # that attention on tensor cores for portions of SINK_MMA_ROWS rows and more (bfloat16)
         # the fewest query heads, and the fewest items of a query tile on the prompt kernel, among the attention layers
         # that `check_attention` has seen (the plan of a step is shared by its layers)
         self._attn_heads = self._attn_items = 0
@@ -168,6 +170,13 @@ class CudaOps(Ops):
         if self._latent_tc is None:
             self._latent_tc = load("fzb200_latent_tc")
         return self._latent_tc
+
+    @property
+    def seq_tc(self):
+        """The attention with a window, kept first tokens and a sink on tensor cores (bfloat16, prompt portions)."""
+        if self._seq_tc is None:
+            self._seq_tc = load("fzb200_seq_tc")
+        return self._seq_tc
 
     @property
     def seq(self):
@@ -923,6 +932,8 @@ class CudaOps(Ops):
         if self.seq.fz_sink_attention_check(c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim)) != 0:
             raise ValueError(f"attention sizes not supported: {num_heads} heads, {num_kv_heads} kv heads, key size {key_dim}, "
                              f"value size {value_dim} (need heads % kv_heads == 0 and sizes of 1..512)")
+        if self.use_tensor_cores and self.sink_tensor_cores and key_dim == value_dim and key_dim in (64, 128):
+            self.seq_tc       # built and loaded with the model, not at its first step
 
     def _kv_views(self, cache, hkv: int, dk: int, dv: int):
         k, v = cache.keys, cache.values
@@ -974,6 +985,19 @@ class CudaOps(Ops):
         # their key and value loads. (float32 keeps the one arithmetic for every step: a position's bits do not depend
         # on the cutting.)
         max_portion = max(1, int(getattr(meta, "max_portion", 0)) or n)
+        n_seg = getattr(meta, "max_segments", meta.n_segments)
+        # prompt portions (bfloat16, keys and values of size 64 or 128): tiles of 64 rows on tensor cores
+        if self.use_tensor_cores and self.sink_tensor_cores and self.dtype == torch.bfloat16 and max_portion >= SINK_MMA_ROWS and \
+                key_dim == value_dim and key_dim in (64, 128) and self.seq_tc.fz_sink_attention_mma_check(
+                    c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim), _p(k), _p(v), c_longlong(k.stride(0)),
+                    c_longlong(k.stride(1)), c_longlong(k.stride(2))) == 0:
+            self._check(self.seq_tc.fz_sink_attention_mma(
+                _p(q), _p(k), _p(v), _p(meta.seg), _p(meta.seq_row), c_int(n_seg), c_int(max_portion), _p(table),
+                c_int(table.shape[1]), c_longlong(k.stride(0)), c_longlong(k.stride(1)), c_longlong(k.stride(2)),
+                c_int(cache.page_size), c_int(k.shape[0]), _p(out), c_int(n), c_int(num_heads), c_int(num_kv_heads),
+                c_int(key_dim), c_float(scale), c_int(window), c_int(keep_first), _p(sink), _p(self.err), self._stream()),
+                "sink_attention (tensor cores)", nbytes)
+            return
         unit_chunks = units = 0
         part = None
         if self.split_decode_keys and self.dtype == torch.bfloat16 and max_portion == 1:

@@ -68,7 +68,7 @@ LARGER = {
     "architecture": "Gizulorn", "vocab": 512, "width": 384, "norm": {"eps": 1e-5},
     "layers": [
         {"type": "retention", "mixer": _ret(6, 64, 64, [0.9, 0.96875, 0.99, 0.996, 0.999, 1.0], 1e6, 64), "mlp": _moe(8, 2, 128, 4, 2, 192)},
-        {"type": "parallel", "mixer": _par(_left(12, 3, 64, 32, 0.125, 100, 5, _rot(250000.0, 32, (8.0, 1.0, 4.0, 256))),
+        {"type": "parallel", "mixer": _par(_left(12, 3, 64, 64, 0.125, 100, 5, _rot(250000.0, 32, (8.0, 1.0, 4.0, 256))),
                                           _right(6, 3, 48, 64, 4), 0.8, 0.5), "mlp": {"kind": "dense", "ff": 640}},
         {"type": "retention", "mixer": _ret(3, 128, 128, [0.98, 0.995, 0.9995], 10000.0, 128), "mlp": _moe(16, 4, 64, 1, 1, 0)},
     ]}
