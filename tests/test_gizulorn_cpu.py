@@ -155,3 +155,23 @@ def test_greedy_generation_through_the_entry_point(dirs):
         for i, t in enumerate(new):
             row = lg[len(prompt) - 1 + i]
             assert int(row.argmax()) == t or row.max() - row[t] < 1e-3
+
+
+def test_command_line_writes_a_preset_and_the_engine_loads_it(tmp_path):
+    import os
+    from fusezap_core_b200.cli import main, presets
+    from fusezap_core_b200.weights.safetensors_io import read_model_dir
+    assert "tiny-gizulorn" in presets()
+    out = str(tmp_path / "m")
+    assert main(["random-weights", "--preset", "tiny-gizulorn", "--out", out, "--seed", "4", "--dtype", "float32", "--num-layers", "2"]) == 0
+    with open(os.path.join(out, "config.json")) as f:
+        cfg = json.load(f)
+    assert [L["type"] for L in cfg["layers"]] == ["retention", "parallel"]
+    w = read_model_dir(out)
+    model, cache, runner = engine_parts(out)
+    toks = tokens_for(cfg, (19,), seed=6)[0]
+    got = run_cut(runner, cache, "r", toks, [6, 1, 12])
+    assert np.isfinite(got).all() and got.shape == (19, 512)
+    # weights of N(0, 0.02) make small logits: the difference is judged against the residual's size, not theirs
+    ref = plain_gizulorn.forward(cfg, w, toks)[0].numpy()
+    assert np.abs(got - ref).max() <= 1e-5 * max(1.0, np.abs(ref).max())

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 import plain_gizulorn
-from gizulorn_util import CONFIGS, make_dir, rounded, tokens_for
+from gizulorn_util import CONFIGS, _left, _moe, _par, _ret, _right, _rot, make_dir, rounded, tokens_for
 from pepilix_util import rel_rms, run_cut, run_mixed
 from fusezap_core_b200.cache import CacheManager
 from fusezap_core_b200.engine import StepRunner, load_model
@@ -463,3 +463,77 @@ def test_greedy_generation_through_the_entry_point(dirs, dtype):
         for i, t in enumerate(new):
             row = lg[len(prompt) - 1 + i]
             assert int(row.argmax()) == t or row.max() - row[t] < margin, (dtype, i, t)
+
+
+def test_command_line_generates_from_a_preset_with_random_weights(capsys):
+    import json
+    from fusezap_core_b200.cli import main
+    assert main(["generate", "--random", "tiny-gizulorn", "--prompt-lens", "5,40,1", "--max-tokens", "6", "--ignore-eos",
+                 "--max-model-len", "128", "--num-blocks", "32", "--max-num-seqs", "2"]) == 0
+    lines = [json.loads(x) for x in capsys.readouterr().out.splitlines() if x.startswith("{")]
+    assert [o["num_prompt_tokens"] for o in lines] == [5, 40, 1]
+    assert all(len(o["token_ids"]) == 6 and o["finish_reason"] == "length" for o in lines)
+
+
+def _random_config(seed: int) -> dict:
+    """A configuration drawn from a seed: odd and even sizes, either layer type in any order, grouped and ungrouped heads,
+    partly rotated heads with and without scaled frequencies, windows from a few tokens to longer than the sequence,
+    dense feed-forwards, routed ones and none."""
+    rng = np.random.default_rng(seed)
+    pick = lambda *xs: xs[int(rng.integers(len(xs)))]
+    width = int(pick(24, 40, 56, 72, 100))
+
+    def rot(dim):
+        dims = int(pick(0, 2, dim // 2 * 2, max(2, dim // 4 * 2)))
+        scaling = pick(None, (4.0, 1.0, 4.0, 32), (8.0, 1.0, 2.0, 16))
+        return _rot(float(pick(50.0, 10000.0, 1e6)), dims, scaling if dims else None)
+
+    def mlp():
+        kind = pick("dense", "moe", "moe", None)
+        if kind is None:
+            return None
+        if kind == "dense":
+            return {"kind": "dense", "ff": int(pick(16, 36, 64))}
+        groups = int(pick(1, 2, 3))
+        per = int(pick(1, 2, 3))
+        keep = int(rng.integers(1, groups + 1))
+        top = int(rng.integers(1, keep * per + 1))
+        return _moe(groups * per, top, int(pick(8, 20, 32)), groups, keep, int(pick(0, 16, 24)))
+
+    layers = []
+    for _ in range(int(rng.integers(1, 4))):
+        if rng.random() < 0.5:
+            H, dk, dv = int(pick(1, 2, 3)), int(pick(6, 8, 16, 20, 36)), int(pick(4, 7, 16, 24))
+            m = _ret(H, dk, dv, [float(pick(0.5, 0.9, 0.99, 1.0)) for _ in range(H)], 1.0, 0)
+            m["rot"] = rot(dk)
+            layers.append({"type": "retention", "mixer": m, "mlp": mlp()})
+        else:
+            kv = int(pick(1, 2))
+            dk, dv = int(pick(8, 12, 16, 40)), int(pick(4, 8, 12, 40))
+            left = _left(kv * int(pick(1, 2, 3)), kv, dk, dv, float(pick(0.2, 0.35)), int(pick(3, 7, 16, 200)), int(pick(0, 1, 5, 9)), rot(dk))
+            kh = int(pick(1, 2))
+            right = _right(kh * int(pick(1, 2)), kh, int(pick(4, 9, 16, 24)), int(pick(3, 8, 20)), int(pick(1, 2, 4, 5)))
+            layers.append({"type": "parallel", "mixer": _par(left, right, float(pick(0.5, 1.0)), float(pick(0.25, 1.5))), "mlp": mlp()})
+    return {"architecture": "Gizulorn", "vocab": int(pick(37, 64, 150)), "width": width, "norm": {"eps": float(pick(1e-6, 1e-5))},
+            "layers": layers}
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Every size and constant comes from the configuration: eight drawn ones, in float32 against the plain model (whole,
+    in portions, token by token), and in bfloat16."""
+    cfg = _random_config(seed)
+    d, cfg, w = make_dir(f"drawn{seed}", tmp_path, cfg, seed)
+    toks = tokens_for(cfg, (45,), seed=seed)[0]
+    for dtype in ("float32", "bfloat16"):
+        model, cache, runner = engine_parts(d, dtype, page=4, pages=30, slots=2, max_len=64)
+        ref = oracle(cfg, w, toks, dtype)
+        for cuts in ((45,), (1,), (6, 2, 1, 17)):
+            got = run_cut(runner, cache, "r", toks, cuts)
+            model.ops.check_errors()
+            agrees(got, ref, dtype, (seed, dtype, cuts, json_of(cfg)))
+
+
+def json_of(cfg):
+    import json
+    return json.dumps(cfg)[:400]
